@@ -36,7 +36,26 @@ def test_reading_a_cache_that_nobody_owns_is_refused():
     with pytest.raises(CacheError, match="owns none"):
         make([CallCacheSpec(state=STATE), CallCacheSpec(kv=FULL, kv_owner=0)])
     with pytest.raises(CacheError, match="different layout"):
-        make([CallCacheSpec(kv=FULL), CallCacheSpec(kv=WIN, kv_owner=0)])
+        make([CallCacheSpec(kv=FULL), CallCacheSpec(kv=KVRequest(2, 32, 0), kv_owner=0)])
+    with pytest.raises(CacheError, match="different layout"):
+        make([CallCacheSpec(kv=FULL), CallCacheSpec(kv=KVRequest(2, 16, 0, value_dim=8), kv_owner=0)])
+
+
+def test_a_reader_may_have_a_window_of_its_own():
+    """The storage keeps what the widest of owner and readers sees; each call is told its own window."""
+    narrow, wide = KVRequest(2, 16, 20), KVRequest(2, 16, 50)
+    c = make([CallCacheSpec(kv=narrow), CallCacheSpec(kv=wide, kv_owner=0), CallCacheSpec(kv=narrow)])
+    assert c.kv_view(0).window == 20 and c.kv_view(1).window == 50 and c.kv_view(2).window == 20
+    assert c.kv_view(0).group != c.kv_view(2).group         # call 2 may drop pages that call 1 still reads
+    assert c.groups[c.kv_view(0).group].request.window == 50 and c.groups[c.kv_view(2).group].request.window == 20
+    s = c.alloc_slots(1)
+    c.reserve(s, [100])
+    c.advance(s, [100])       # the next query, position 100, sees keys from 51 (wide) or 81 (narrow)
+    assert len(c.groups[c.kv_view(0).group].pages_held(s[0])) == 7 - 3      # pages 0..2 (keys < 48) are gone
+    assert len(c.groups[c.kv_view(2).group].pages_held(s[0])) == 7 - 5      # pages 0..4 (keys < 80) are gone
+    # a reader that sees everything keeps everything
+    c = make([CallCacheSpec(kv=narrow), CallCacheSpec(kv=FULL, kv_owner=0)])
+    assert c.groups[0].request.window == 0 and c.kv_view(0).window == 20 and c.kv_view(1).window == 0
 
 
 def test_slots_and_pages_go_round():

@@ -23,7 +23,7 @@ All bookkeeping is host-side Python on NumPy tables; only `sync()` touches the d
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Optional, Sequence
 
 import numpy as np
@@ -151,19 +151,26 @@ class CacheManager:
         self._kv_place: dict[int, tuple[int, int]] = {}          # owning call -> (group, layer in group)
         self._kv_of_call: dict[int, int] = {}                    # call -> owning call
         by_request: dict[KVRequest, list[int]] = {}
+        self._window_of_call: dict[int, int] = {}
         for c, spec in enumerate(calls):
             if spec.kv is None:
                 continue
-            owner = c if spec.kv_owner is None else spec.kv_owner
-            self._kv_of_call[c] = owner
-            if owner == c:
-                by_request.setdefault(spec.kv, []).append(c)
+            self._kv_of_call[c] = c if spec.kv_owner is None else spec.kv_owner
+            self._window_of_call[c] = spec.kv.window
+        # A reader may look further back than the call whose cache it reads (or not at all as far): the
+        # storage keeps what the widest of them sees (window 0 = everything), each call masks for itself.
+        keep: dict[int, int] = {}
         for c, owner in self._kv_of_call.items():
             if owner != c:
                 if owner not in self._kv_of_call or self._kv_of_call[owner] != owner:
                     raise CacheError(f"call {c} reads the cache of call {owner}, which owns none")
-                if calls[owner].kv != calls[c].kv:
+                if replace(calls[owner].kv, window=0) != replace(calls[c].kv, window=0):
                     raise CacheError(f"call {c} reads the cache of call {owner} but asks for a different layout")
+            w = calls[c].kv.window
+            keep[owner] = w if owner not in keep else (0 if w <= 0 or keep[owner] <= 0 else max(keep[owner], w))
+        for c, owner in self._kv_of_call.items():
+            if owner == c:
+                by_request.setdefault(replace(calls[c].kv, window=keep[c]), []).append(c)
         for request, owners in by_request.items():
             g = len(self.groups)
             self.groups.append(KVGroup(request, len(owners), self.num_pages, page_size, max_slots,
@@ -192,7 +199,7 @@ class CacheManager:
         g, i = self._kv_place[self._kv_of_call[call]]
         grp = self.groups[g]
         return KVView(grp.k[i], None if grp.v is None else grp.v[i], grp.table_dev, self.page_size,
-                      grp.request.window, g)
+                      self._window_of_call[call], g)
 
     def writes_kv(self, call: int) -> bool:
         return self._kv_of_call.get(call) == call

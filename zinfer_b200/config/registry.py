@@ -34,10 +34,15 @@ def registered_architectures() -> list[str]:
 
 
 def architecture_name(config_dict: dict) -> str:
+    """`architectures[0]`, or the string under `architecture` in files that name one model class."""
     archs = config_dict.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: required key 'architectures' (a list naming the model class) is missing")
-    return archs[0]
+    if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = config_dict.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: required key 'architectures' (a list naming the model class; or 'architecture', "
+                      "its name) is missing")
 
 
 def get_architecture(name: str) -> Architecture:

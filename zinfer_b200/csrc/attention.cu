@@ -193,6 +193,69 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   }
 }
 
+// The same step for a mixer whose q and k norms run over the WHOLE projection (all heads of a
+// token at once, weight of that width) and whose values may have another width than its keys;
+// no rotation.  A row of `qkv` holds [q (H * hd) | k (Hkv * hd) | v (Hkv * vd)], or q alone when
+// the call reads another call's cache (write_kv = 0).  One block per token; sums of squares are
+// float32 and added in an order that the thread layout alone fixes.
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+    qk_prepare_span_kernel(const T* __restrict__ qkv, int ld, T* __restrict__ q_out, T* __restrict__ k_cache,
+                           T* __restrict__ v_cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                           const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                           const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
+                           int Hkv, int hd, int vd, float eps, int page_size, int write_kv, int* status) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();   // qkv is the kernel before's result
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int qd = H * hd, kd = Hkv * hd;
+  const T* row = qkv + (size_t)t * ld;
+  float scale = 1.f;
+  if (q_w) {
+    float ss = 0.f;
+    for (int d = tid; d < qd; d += blockDim.x) {
+      const float v = to_f32(row[d]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    scale = 1.0f / sqrtf(ss / (float)qd + eps);
+  }
+  for (int d = tid; d < qd; d += blockDim.x) {
+    const float v = to_f32(row[d]);
+    q_out[(size_t)t * qd + d] = from_f32<T>(q_w ? (v * scale) * q_w[d] : v);
+  }
+  if (!write_kv) return;
+  const int pos = tok_pos[t];
+  const int page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
+  if (page < 0) {
+    if (tid == 0) atomicExch(status, 2);
+    return;
+  }
+  const T* krow = row + qd;
+  float kscale = 1.f;
+  if (k_w) {
+    float ss = 0.f;
+    for (int d = tid; d < kd; d += blockDim.x) {
+      const float v = to_f32(krow[d]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    kscale = 1.0f / sqrtf(ss / (float)kd + eps);
+  }
+  const int in_page = pos % page_size;
+  for (int d = tid; d < kd; d += blockDim.x) {
+    const float v = to_f32(krow[d]);
+    const int kh = d / hd, e = d - kh * hd;
+    k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] = from_f32<T>(k_w ? (v * kscale) * k_w[d] : v);
+  }
+  const T* vrow = krow + kd;
+  for (int d = tid; d < Hkv * vd; d += blockDim.x) {
+    const int kh = d / vd, e = d - kh * vd;
+    v_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * vd + e] = vrow[d];
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // (2) attention.  Block = (query tile, kv head x head chunk, key split).  A query tile is
 // `bq` consecutive tokens of one sequence; its rows are (token, head in group) pairs, at
@@ -205,12 +268,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, const int* __restrict__ cu_q,
                     const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                     const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd,
-                    int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys) {
+                    int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
+                    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2) {
+  // vd: width of a value row (the keys' width is hd); NPL covers vd.  bias_r1 / bias_r2 [H]: with both
+  // given, r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query i and key j (float32).
   extern __shared__ float smem[];
   float* qs = smem;                               // [ATT_ROWS][hd]
   float* Ks = qs + ATT_ROWS * hd;                 // [ATT_TK][hd + 1]
-  float* Vs = Ks + ATT_TK * (hd + 1);             // [ATT_TK][hd]
-  long long* rowoff = reinterpret_cast<long long*>(Vs + ATT_TK * hd);  // [ATT_TK]
+  float* Vs = Ks + ATT_TK * (hd + 1);             // [ATT_TK][vd]
+  long long* rowoff = reinterpret_cast<long long*>(Vs + ATT_TK * vd + ((ATT_TK * (hd + 1) + ATT_TK * vd) & 1));  // [ATT_TK], 8-byte aligned
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = H / Hkv;
@@ -236,6 +302,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     row_hi[i] = start + q0 + tq + 1;
     row_lo[i] = (window > 0 && row_hi[i] > window) ? row_hi[i] - window : 0;
   }
+  float r1[4], r2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    r1[i] = (bias_r1 && row_ok[i]) ? bias_r1[row_h[i]] : 0.f;
+    r2[i] = (bias_r2 && row_ok[i]) ? bias_r2[row_h[i]] : 0.f;
+  }
+  const bool biased = bias_r1 != nullptr && bias_r2 != nullptr;
 
   // stage the query rows as float32
   for (int idx = tid; idx < ATT_ROWS * hd; idx += ATT_WARPS * 32) {
@@ -276,7 +349,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       long long off = -1;
       if (kp < k_end) {
         const int page = pt[kp / page_size];
-        if (page >= 0) off = (((long long)page * Hkv + kvh) * page_size + kp % page_size) * hd;
+        if (page >= 0) off = ((long long)page * Hkv + kvh) * page_size + kp % page_size;   // row index; x hd or vd below
       }
       rowoff[tid] = off;
     }
@@ -284,13 +357,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     for (int idx = tid; idx < ATT_TK * hd; idx += ATT_WARPS * 32) {
       const int j = idx / hd, d = idx - j * hd;
       const long long off = rowoff[j];
-      float kv = 0.f, vv = 0.f;
-      if (off >= 0) {
-        kv = to_f32(k_cache[off + d]);
-        vv = to_f32(v_cache[off + d]);
-      }
-      Ks[j * (hd + 1) + d] = kv;
-      Vs[j * hd + d] = vv;
+      Ks[j * (hd + 1) + d] = off >= 0 ? to_f32(k_cache[off * hd + d]) : 0.f;
+    }
+    for (int idx = tid; idx < ATT_TK * vd; idx += ATT_WARPS * 32) {
+      const int j = idx / vd, d = idx - j * vd;
+      const long long off = rowoff[j];
+      Vs[j * vd + d] = off >= 0 ? to_f32(v_cache[off * vd + d]) : 0.f;
     }
     __syncthreads();
 
@@ -307,7 +379,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const bool ok = row_ok[i] && key_ok && kp >= row_lo[i] && kp < row_hi[i];
-      const float sc = ok ? s[i] * scale : -INFINITY;
+      float sc = -INFINITY;
+      if (ok) {
+        sc = s[i] * scale;
+        if (biased) sc -= r1[i] * log1pf(r2[i] * (float)(row_hi[i] - 1 - kp));
+      }
       const float mt = warp_max(sc);
       if (mt == -INFINITY) {  // no key of this tile is visible to this row
         p[i] = 0.f;
@@ -326,7 +402,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
       for (int c = 0; c < NPL; ++c) {
         const int d = lane + 32 * c;
-        vj[c] = d < hd ? Vs[j * hd + d] : 0.f;
+        vj[c] = d < vd ? Vs[j * vd + d] : 0.f;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -342,19 +418,19 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     if (!row_ok[i]) continue;
     if (num_splits == 1) {
       const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
-      T* dst = out + (size_t)row_t[i] * H * hd + (size_t)row_h[i] * hd;
+      T* dst = out + (size_t)row_t[i] * H * vd + (size_t)row_h[i] * vd;
 #pragma unroll
       for (int c = 0; c < NPL; ++c) {
         const int d = lane + 32 * c;
-        if (d < hd) dst[d] = from_f32<T>(o[i][c] * inv);
+        if (d < vd) dst[d] = from_f32<T>(o[i][c] * inv);
       }
     } else {
       const size_t row = ((size_t)split * n_tokens + row_t[i]) * H + row_h[i];
-      float* dst = part_o + row * hd;
+      float* dst = part_o + row * vd;
 #pragma unroll
       for (int c = 0; c < NPL; ++c) {
         const int d = lane + 32 * c;
-        if (d < hd) dst[d] = o[i][c];
+        if (d < vd) dst[d] = o[i][c];
       }
       if (lane == 0) {
         part_ml[row * 2] = m[i];
@@ -420,16 +496,17 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 namespace {
 
-size_t attn_smem_bytes(int hd) {
-  return sizeof(float) * ((size_t)ATT_ROWS * hd + (size_t)ATT_TK * (hd + 1) + (size_t)ATT_TK * hd) + sizeof(long long) * ATT_TK + 16;
+size_t attn_smem_bytes(int hd, int vd) {
+  return sizeof(float) * ((size_t)ATT_ROWS * hd + (size_t)ATT_TK * (hd + 1) + (size_t)ATT_TK * vd + 1) + sizeof(long long) * ATT_TK + 16;
 }
 
 template <typename T, int NPL>
 int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
-                int window, float scale, int bq, int gc, int num_splits, int split_keys, cudaStream_t stream) {
-  const size_t smem = attn_smem_bytes(hd);
+                int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd, const float* r1,
+                const float* r2, cudaStream_t stream) {
+  const size_t smem = attn_smem_bytes(hd, vd);
   auto kern = attn_fwd_kernel<T, NPL>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -441,7 +518,7 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
   kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_o,
                                                part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
                                                pt_stride, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,
-                                               num_splits, split_keys);
+                                               num_splits, split_keys, vd, r1, r2);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -449,14 +526,14 @@ template <typename T>
 int dispatch_attn(int hd, const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
                   float* part_ml, const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start,
                   const int* seq_slot, const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv,
-                  int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys,
-                  cudaStream_t stream) {
+                  int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
+                  const float* r1, const float* r2, cudaStream_t stream) {
 #define ZK_ATT_CASE(N)                                                                                               \
   case N:                                                                                                            \
     return launch_attn<T, N>(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, \
                              page_table, pt_stride, n_tiles, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,  \
-                             num_splits, split_keys, stream);
-  switch ((hd + 31) / 32) {
+                             num_splits, split_keys, vd, r1, r2, stream);
+  switch ((vd + 31) / 32) {
     ZK_ATT_CASE(1) ZK_ATT_CASE(2) ZK_ATT_CASE(3) ZK_ATT_CASE(4) ZK_ATT_CASE(5) ZK_ATT_CASE(6) ZK_ATT_CASE(7)
     ZK_ATT_CASE(8)
   }
@@ -509,25 +586,46 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
   return ZK_LAUNCH_STATUS();
 }
 
-// q, out [n_tokens, H*hd]; part_o [num_splits, n_tokens*H, hd] and part_ml [num_splits,
+// q/k RMSNorm over the whole projection (weights [H*hd] and [Hkv*hd], either may be null), values vd wide.
+// qkv rows are `ld` elements apart and hold q alone when write_kv = 0.
+int zk_qk_prepare_span(const void* qkv, int ld, void* q_out, void* k_cache, void* v_cache, const float* q_w,
+                       const float* k_w, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                       const int* page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd, int vd, float eps,
+                       int page_size, int write_kv, int dtype, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd <= 0 || vd <= 0 || H <= 0 || Hkv <= 0 || page_size <= 0) return ZK_EINVAL;
+  if (ld < H * hd + (write_kv ? Hkv * (hd + vd) : 0)) return ZK_EINVAL;
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(qk_prepare_span_kernel<float>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,
+        (const float*)qkv, ld, (float*)q_out, (float*)k_cache, (float*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, write_kv, status);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(qk_prepare_span_kernel<bf16>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,
+        (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, write_kv, status);
+  return ZK_EINVAL;
+}
+
+// q [n_tokens, H*hd], out [n_tokens, H*vd]; part_o [num_splits, n_tokens*H, hd] and part_ml [num_splits,
 // n_tokens*H, 2] float32 scratch, used when num_splits > 1 (then call zk_attn_merge).
 int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
-                int window, float scale, int bq, int gc, int num_splits, int split_keys, int dtype,
-                cudaStream_t stream) {
+                int window, float scale, int bq, int gc, int num_splits, int split_keys, int dtype, int vd,
+                const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
   if (n_tiles <= 0 || n_tokens <= 0) return 0;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0) return ZK_EINVAL;
+  if (vd <= 0 || vd > ATT_MAX_HD || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
   if (gc <= 0 || gc > ATT_ROWS || bq <= 0 || bq * gc > ATT_ROWS || num_splits < 1) return ZK_EINVAL;
   if (num_splits > 1 && (split_keys <= 0 || split_keys % ATT_TK || !part_o || !part_ml)) return ZK_EINVAL;
   if (dtype == ZK_F32)
     return dispatch_attn<float>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                 seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale,
-                                bq, gc, num_splits, split_keys, stream);
+                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, stream);
   if (dtype == ZK_BF16)
     return dispatch_attn<bf16>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale, bq,
-                               gc, num_splits, split_keys, stream);
+                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, stream);
   return ZK_EINVAL;
 }
 

@@ -5,9 +5,12 @@
 
 // x[t, :] = float(table[tokens[t], :]).  A token id outside [0, vocab) sets *status = 1 and
 // yields a zero row (reference: row lookup of token_embd, src/model.zig:2352-2358).
+// With `pos_table` [max_pos, dim] a learned position vector is added, unscaled, in float32:
+// x[t, :] += float(pos_table[tok_pos[t], :]); a position outside the table sets *status = 3.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
-                             int dim, int vocab, float scale, int* status) {
+                             int dim, int vocab, float scale, int* status, const T* __restrict__ pos_table,
+                             const int* __restrict__ tok_pos, int max_pos) {
   zk_let_next_start();
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int t = blockIdx.x;
@@ -16,7 +19,17 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
   if (!ok && threadIdx.x == 0) atomicExch(status, 1);
   const T* row = table + (size_t)(ok ? tok : 0) * dim;
   float* out = x + (size_t)t * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) out[d] = ok ? to_f32(row[d]) * scale : 0.f;
+  const T* prow = nullptr;
+  if (pos_table) {
+    const int p = tok_pos[t];
+    if (p >= 0 && p < max_pos) prow = pos_table + (size_t)p * dim;
+    else if (threadIdx.x == 0) atomicExch(status, 3);
+  }
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float v = ok ? to_f32(row[d]) * scale : 0.f;
+    if (prow) v += to_f32(prow[d]);
+    out[d] = v;
+  }
 }
 
 // y[r, :] = (x[src(r), :] * rsqrt(mean(x^2) + eps)) * w   (src/model.zig:1166-1181: scale
@@ -118,6 +131,112 @@ __global__ void fill_normal_kernel(T* __restrict__ out, size_t n, unsigned long 
   }
 }
 
+// x[r, :] += (m[r, :] * rsqrt(mean(m^2) + eps)) * w: the RMSNorm of a sublayer's OUTPUT added to
+// the residual rows, all in float32.  One block per row; the row of m stays in registers when it
+// fits (16 values per thread), else it is read twice.
+__global__ void rmsnorm_add_kernel(const float* __restrict__ m, const float* __restrict__ w, float* __restrict__ x,
+                                   int dim, float eps) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int r = blockIdx.x;
+  const float* mr = m + (size_t)r * dim;
+  float* xr = x + (size_t)r * dim;
+  float keep[16];
+  const bool fits = dim <= 16 * (int)blockDim.x;
+  float ss = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      keep[i] = d < dim ? mr[d] : 0.f;
+      ss = fmaf(keep[i], keep[i], ss);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) ss = fmaf(mr[d], mr[d], ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) xr[d] += (keep[i] * scale) * w[d];
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) xr[d] += (mr[d] * scale) * w[d];
+  }
+}
+
+// Activations of a plain (ungated) feed-forward, float32 arithmetic:
+// 0 = gelu with erf: 0.5 z (1 + erf(z / sqrt 2)); 1 = gelu with tanh:
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2 = silu; 3 = relu.
+__device__ __forceinline__ float zk_activate(float z, int kind) {
+  switch (kind) {
+    case 0: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    case 1: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    case 2: return z / (1.0f + expf(-z));
+    default: return fmaxf(z, 0.f);
+  }
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, int kind) {
+  zk_let_next_start();
+  zk_wait_prior();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(zk_activate(to_f32(in[i]), kind));
+}
+
+// Float32 rows in the run dtype (the input of a contraction that reads the residual rows as they are).
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ out, size_t total) {
+  zk_let_next_start();
+  zk_wait_prior();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(in[i]);
+}
+
+// logits <- cap * tanh(logits / cap), in place, float32.
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const float inv = 1.0f / cap;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
+}
+
+// out = sum_{j < n_terms} w[j] * planes[j], planes [n_terms (or more), plane] float32 one behind the
+// other `plane` elements apart, added in the order of j.  n_terms = 1 with w = nullptr copies.
+__global__ void weighted_sum_kernel(const float* __restrict__ planes, const float* __restrict__ w, int n_terms,
+                                    size_t plane, float* __restrict__ out) {
+  zk_let_next_start();
+  zk_wait_prior();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.x * blockDim.x) {
+    float acc = (w ? w[0] : 1.0f) * planes[i];
+    for (int j = 1; j < n_terms; ++j) acc = fmaf(w[j], planes[(size_t)j * plane + i], acc);
+    out[i] = acc;
+  }
+}
+
+// m[t, :] += sigmoid(x[t, :] . g) * s[t, :]: a branch s that every token takes, weighed by one
+// number per token that a gate vector g [dim] gives.  Float32 throughout; one block per token.
+__global__ void gate_add_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ s,
+                                float* __restrict__ m, int dim, int out_dim) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x;
+  const float* xr = x + (size_t)t * dim;
+  float dot = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dot = fmaf(xr[d], g[d], dot);
+  dot = block_sum(dot, scratch);
+  const float gate = 1.0f / (1.0f + expf(-dot));
+  const float* sr = s + (size_t)t * out_dim;
+  float* mr = m + (size_t)t * out_dim;
+  for (int d = threadIdx.x; d < out_dim; d += blockDim.x) mr[d] = fmaf(gate, sr[d], mr[d]);
+}
+
 extern "C" {
 
 int zk_fill_normal(void* out, long long n, long long seed, float mean, float std, int dtype, cudaStream_t stream) {
@@ -141,14 +260,16 @@ const char* zk_error_name(int code) {
 }
 
 int zk_embed(const int* tokens, const void* table, float* x, int n, int dim, int vocab, float scale, int dtype,
-             int* status, cudaStream_t stream) {
+             int* status, const void* pos_table, const int* tok_pos, int max_pos, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (dim <= 0 || vocab <= 0) return ZK_EINVAL;
+  if (dim <= 0 || vocab <= 0 || (pos_table && (!tok_pos || max_pos <= 0))) return ZK_EINVAL;
   const int threads = dim >= 1024 ? 256 : 128;
   if (dtype == ZK_F32)
-    embed_kernel<float><<<n, threads, 0, stream>>>(tokens, (const float*)table, x, dim, vocab, scale, status);
+    embed_kernel<float><<<n, threads, 0, stream>>>(tokens, (const float*)table, x, dim, vocab, scale, status,
+                                                   (const float*)pos_table, tok_pos, max_pos);
   else if (dtype == ZK_BF16)
-    embed_kernel<bf16><<<n, threads, 0, stream>>>(tokens, (const bf16*)table, x, dim, vocab, scale, status);
+    embed_kernel<bf16><<<n, threads, 0, stream>>>(tokens, (const bf16*)table, x, dim, vocab, scale, status,
+                                                  (const bf16*)pos_table, tok_pos, max_pos);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
@@ -189,6 +310,62 @@ int zk_silu_mul(const void* gu, void* h, int n, int F, int il, int dtype, cudaSt
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
+}
+
+static inline int grid_for_total(size_t total, int threads) {
+  const size_t want = (total + threads - 1) / threads;
+  return (int)(want < 148 * 16 ? want : 148 * 16);
+}
+
+int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim <= 0) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  return zk_launch_dependent(rmsnorm_add_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps);
+}
+
+int zk_activation(const void* in, void* out, long long total, int kind, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (kind < 0 || kind > 3) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)total, threads);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(activation_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, (size_t)total, kind);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)in, (bf16*)out, (size_t)total, kind);
+  return ZK_EINVAL;
+}
+
+int zk_cast_rows(const float* in, void* out, long long total, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256, blocks = grid_for_total((size_t)total, threads);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(cast_rows_kernel<float>, dim3(blocks), dim3(threads), 0, stream, in, (float*)out, (size_t)total);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(cast_rows_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, in, (bf16*)out, (size_t)total);
+  return ZK_EINVAL;
+}
+
+int zk_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)total, threads);
+  return zk_launch_dependent(softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, (size_t)total, cap);
+}
+
+int zk_weighted_sum(const float* planes, const float* w, int n_terms, long long plane, float* out, cudaStream_t stream) {
+  if (plane <= 0) return 0;
+  if (n_terms < 1 || (n_terms > 1 && !w)) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)plane, threads);
+  return zk_launch_dependent(weighted_sum_kernel, dim3(blocks), dim3(threads), 0, stream, planes, w, n_terms, (size_t)plane, out);
+}
+
+int zk_gate_add(const float* x, const float* g, const float* s, float* m, int n, int dim, int out_dim, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim <= 0 || out_dim <= 0) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  return zk_launch_dependent(gate_add_kernel, dim3(n), dim3(threads), 0, stream, x, g, s, m, dim, out_dim);
 }
 
 }  // extern "C"

@@ -1,0 +1,178 @@
+// Mixture of small gated feed-forwards whose experts are picked by a TABLE indexed with the token id
+// (no router): token t uses experts table[token_t][0 .. top), each with weight 1/top.
+//   y_t = (1/top) * sum_k W_down[e_k] (silu(W_gate[e_k] x_t) * (W_up[e_k] x_t))
+// Two weight-streaming kernels.  (1) gate/up: one block per (token, k) and slice of the expert's
+// hidden units; a warp owns a hidden unit at a time, its lanes walk the input row, sums in float32,
+// silu in float32.  (2) down: one block per token and slice of the outputs; the `top` experts are
+// added in the order of k, so a token's result does not depend on the rest of the batch.
+// Weights are stacked [experts, rows, cols] in the run dtype; x and h are the run dtype, y float32.
+#include "common.cuh"
+
+#define MOE_WARPS 8
+
+template <typename T> struct Vec8;   // eight consecutive values as float
+template <> struct Vec8<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* o) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      o[2 * i] = f.x;
+      o[2 * i + 1] = f.y;
+    }
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* o) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  }
+};
+
+// dot of a weight row with the row staged in shared memory (float32), lanes striding; VEC: rows are
+// 16-byte aligned and K a multiple of 8.
+template <typename T, bool VEC>
+__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int K, int lane) {
+  float acc = 0.f;
+  if (VEC) {
+    for (int k = lane * 8; k < K; k += 256) {
+      float v[8];
+      Vec8<T>::load(w + k, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf(v[i], xs[k + i], acc);
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), xs[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+__device__ __forceinline__ int moe_expert(const int* __restrict__ tokens, const int* __restrict__ table, int t, int k,
+                                          int top, int vocab, int n_experts, int* status) {
+  int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) tok = 0;        // the embedding kernel has flagged it
+  int e = table[(size_t)tok * top + k];
+  if (e < 0 || e >= n_experts) {
+    if (threadIdx.x == 0) atomicExch(status, 4);
+    e = 0;
+  }
+  return e;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+    moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ table,
+                       const T* __restrict__ w_gate, const T* __restrict__ w_up, T* __restrict__ h, int D, int F,
+                       int top, int vocab, int n_experts, int units_per_block, int* status) {
+  extern __shared__ float xs[];     // [D]
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x / top, k = blockIdx.x % top;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * D + d]);
+  __syncthreads();
+  const T* wg = w_gate + (size_t)e * F * D;
+  const T* wu = w_up + (size_t)e * F * D;
+  const int f0 = blockIdx.y * units_per_block, f1 = min(F, f0 + units_per_block);
+  for (int f = f0 + warp; f < f1; f += MOE_WARPS) {
+    const float g = row_dot<T, VEC>(wg + (size_t)f * D, xs, D, lane);
+    const float u = row_dot<T, VEC>(wu + (size_t)f * D, xs, D, lane);
+    if (lane == 0) h[((size_t)t * top + k) * F + f] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+    moe_down_kernel(const T* __restrict__ h, const int* __restrict__ tokens, const int* __restrict__ table,
+                    const T* __restrict__ w_down, float* __restrict__ y, int D, int F, int top, int vocab,
+                    int n_experts, int outs_per_block, int accumulate, int* status) {
+  extern __shared__ float hs[];     // [top][F]
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * top * F + i]);
+  __syncthreads();
+  const float weight = 1.0f / (float)top;
+  const int d0 = blockIdx.y * outs_per_block, d1 = min(D, d0 + outs_per_block);
+  for (int d = d0 + warp; d < d1; d += MOE_WARPS) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
+      acc += weight * row_dot<T, VEC>(w_down + ((size_t)e * D + d) * F, hs + (size_t)k * F, F, lane);
+    }
+    if (lane == 0) {
+      float* dst = y + (size_t)t * D + d;
+      *dst = accumulate ? *dst + acc : acc;
+    }
+  }
+}
+
+namespace {
+
+template <typename T>
+int launch_moe(const void* x, const int* tokens, const int* table, const void* w_gate, const void* w_up,
+               const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
+               int accumulate, int* status, cudaStream_t stream) {
+  const int per = 16 / (int)sizeof(T);   // elements per 16 bytes
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec_gu = D % 8 == 0 && D % per == 0 && aligned(w_gate) && aligned(w_up);
+  const bool vec_dn = F % 8 == 0 && F % per == 0 && aligned(w_down);
+  // enough blocks to fill the GPU when the tokens are few, whole experts per block when they are many
+  int units = F, outs = D;
+  const long long pairs = (long long)n * top;
+  while (units > MOE_WARPS && pairs * ((F + units - 1) / units) < 2 * 148) units = (units + 1) / 2;
+  while (outs > MOE_WARPS && (long long)n * ((D + outs - 1) / outs) < 2 * 148) outs = (outs + 1) / 2;
+  const size_t smem_gu = sizeof(float) * D, smem_dn = sizeof(float) * (size_t)top * F;
+  if (smem_gu > 200 * 1024 || smem_dn > 200 * 1024) return ZK_EINVAL;
+  const dim3 grid_gu((unsigned)pairs, (F + units - 1) / units), grid_dn(n, (D + outs - 1) / outs);
+  int rc;
+#define ZK_MOE_GU(V)                                                                                                  \
+  do {                                                                                                                \
+    auto kern = moe_gate_up_kernel<T, V>;                                                                             \
+    if (smem_gu > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu);          \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    rc = zk_launch_dependent(kern, grid_gu, dim3(MOE_WARPS * 32), smem_gu, stream, (const T*)x, tokens, table,        \
+                             (const T*)w_gate, (const T*)w_up, (T*)h, D, F, top, vocab, n_experts, units, status);    \
+  } while (0)
+#define ZK_MOE_DN(V)                                                                                                  \
+  do {                                                                                                                \
+    auto kern = moe_down_kernel<T, V>;                                                                                \
+    if (smem_dn > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn);          \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    rc = zk_launch_dependent(kern, grid_dn, dim3(MOE_WARPS * 32), smem_dn, stream, (const T*)h, tokens, table,        \
+                             (const T*)w_down, y, D, F, top, vocab, n_experts, outs, accumulate, status);             \
+  } while (0)
+  if (vec_gu) ZK_MOE_GU(true); else ZK_MOE_GU(false);
+  if (rc != 0) return rc;
+  if (vec_dn) ZK_MOE_DN(true); else ZK_MOE_DN(false);
+  return rc;
+#undef ZK_MOE_GU
+#undef ZK_MOE_DN
+}
+
+}  // namespace
+
+extern "C" {
+
+// x [n, D], h [n, top, F] (scratch, run dtype), y [n, D] float32 (= or += with `accumulate`);
+// tokens [n] and table [vocab, top] int32; w_gate, w_up [experts, F, D], w_down [experts, D, F].
+int zk_moe_table(const void* x, const int* tokens, const int* table, const void* w_gate, const void* w_up,
+                 const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
+                 int accumulate, int dtype, int* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (D <= 0 || F <= 0 || top <= 0 || vocab <= 0 || n_experts <= 0) return ZK_EINVAL;
+  if (dtype == ZK_F32)
+    return launch_moe<float>(x, tokens, table, w_gate, w_up, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+  if (dtype == ZK_BF16)
+    return launch_moe<bf16>(x, tokens, table, w_gate, w_up, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+  return ZK_EINVAL;
+}
+
+}  // extern "C"

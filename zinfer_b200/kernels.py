@@ -24,10 +24,24 @@ _C = {"p": ctypes.c_void_p, "i": ctypes.c_int, "f": ctypes.c_float, "l": ctypes.
 # pointer of every launcher is the stream
 _SIGNATURES = {
     "elementwise": {
-        "zk_embed": "pppiiifipp",
+        "zk_embed": "pppiiifip" + "ppi" + "p",
         "zk_rmsnorm": "ppppiifip",
         "zk_silu_mul": "ppiiiip",
         "zk_fill_normal": "pllffip",
+        "zk_rmsnorm_add": "pppiifp",
+        "zk_activation": "ppliip",
+        "zk_cast_rows": "pplip",
+        "zk_softcap": "plfp",
+        "zk_weighted_sum": "ppilpp",
+        "zk_gate_add": "ppppiiip",
+    },
+    "seqconv": {
+        "zk_seqconv_forward": "ppppppp" + "iiiliiip",
+        "zk_seqconv_state_update": "ppppiiilp",
+        "zk_seqconv_max_taps": "",
+    },
+    "moe": {
+        "zk_moe_table": "pppppppp" + "iiiiiiiipp",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -80,7 +94,8 @@ _SIGNATURES = {
     },
     "attention": {
         "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiipp",
-        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiiip",
+        "zk_qk_prepare_span": "pipppppppppiiiiiifiiipp",
+        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ipp" + "p",
         "zk_attn_merge": "pppiiiip",
         "zk_attn_rows_per_block": "",
         "zk_attn_max_head_dim": "",
@@ -187,16 +202,159 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 # ------------------------------------------------------------------------------- row kernels
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """x[t] = float32(table[tokens[t]]) * scale; bad ids set status to 1."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, status: torch.Tensor, scale: float = 1.0,
+          pos_table: Optional[torch.Tensor] = None, tok_pos: Optional[torch.Tensor] = None,
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[t] = float32(table[tokens[t]]) * scale; bad ids set status to 1.  With `pos_table`
+    [positions, dim] (the table's dtype) the row pos_table[tok_pos[t]] is added, unscaled; a position
+    outside it sets status to 3.  `out`: float32 [n, dim] to write into."""
     _need(tokens, "tokens", torch.int32)
     _need(table, "table", (torch.float32, torch.bfloat16), (None, None))
     _need(status, "status", torch.int32)
     n, (vocab, dim) = tokens.numel(), table.shape
-    x = torch.empty((n, dim), dtype=torch.float32, device=table.device)
-    _check(_fn("elementwise", "zk_embed")(_ptr(tokens), _ptr(table), _ptr(x), n, dim, vocab, scale,
-                                          dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+    max_pos = 0
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype, (None, dim))
+        _need(tok_pos, "tok_pos", torch.int32, (n,))
+        max_pos = pos_table.shape[0]
+    if out is None:
+        out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32, (n, dim))
+    _check(_fn("elementwise", "zk_embed")(_ptr(tokens), _ptr(table), _ptr(out), n, dim, vocab, scale,
+                                          dtype_code(table.dtype), _ptr(status), _ptr(pos_table), _ptr(tok_pos), max_pos,
+                                          _stream()), "embed")
+    return out
+
+
+def rmsnorm_add(m: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor) -> torch.Tensor:
+    """x += RMSNorm(m) * weight, row by row, all float32: the norm of a sublayer's output summed into
+    the residual rows."""
+    _need(m, "m", torch.float32, (None, None))
+    _need(x, "x", torch.float32, tuple(m.shape))
+    _need(weight, "weight", torch.float32, (m.shape[1],))
+    _check(_fn("elementwise", "zk_rmsnorm_add")(_ptr(m), _ptr(weight), _ptr(x), m.shape[0], m.shape[1], eps, _stream()),
+           "rmsnorm_add")
     return x
+
+
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def activation(z: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(z) elementwise in float32 arithmetic; kind is one of ACTIVATIONS ("gelu" is the erf form)."""
+    _need(z, "z", (torch.float32, torch.bfloat16))
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r}; known: {sorted(ACTIVATIONS)}")
+    if out is None:
+        out = torch.empty_like(z)
+    _need(out, "out", z.dtype, tuple(z.shape))
+    _check(_fn("elementwise", "zk_activation")(_ptr(z), _ptr(out), z.numel(), ACTIVATIONS[kind], dtype_code(z.dtype),
+                                               _stream()), "activation")
+    return out
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Float32 rows in the run dtype (the rows themselves when that is float32)."""
+    _need(x, "x", torch.float32)
+    if dtype == torch.float32:
+        return x
+    y = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(_fn("elementwise", "zk_cast_rows")(_ptr(x), _ptr(y), x.numel(), dtype_code(dtype), _stream()), "cast_rows")
+    return y
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place: logits <- cap * tanh(logits / cap), float32."""
+    _need(logits, "logits", torch.float32)
+    _check(_fn("elementwise", "zk_softcap")(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
+    return logits
+
+
+def weighted_sum(planes: torch.Tensor, weights: Optional[torch.Tensor], n_terms: int, out: torch.Tensor) -> torch.Tensor:
+    """out = sum_{j < n_terms} weights[j] * planes[j], added in the order of j; planes float32
+    [>= n_terms, ...] contiguous, weights float32 [>= n_terms] on the device (None with n_terms 1: a copy)."""
+    _need(planes, "planes", torch.float32)
+    if planes.dim() < 2 or planes.shape[0] < n_terms or n_terms < 1:
+        raise KernelError(f"weighted_sum: {n_terms} terms of planes {tuple(planes.shape)}")
+    _need(out, "out", torch.float32, tuple(planes.shape[1:]))
+    if weights is not None:
+        _need(weights, "weights", torch.float32)
+        if weights.numel() < n_terms:
+            raise KernelError(f"weighted_sum: {weights.numel()} weights for {n_terms} terms")
+    elif n_terms != 1:
+        raise KernelError("weighted_sum: several terms need weights")
+    _check(_fn("elementwise", "zk_weighted_sum")(_ptr(planes), _ptr(weights), n_terms, out.numel(), _ptr(out), _stream()),
+           "weighted_sum")
+    return out
+
+
+def gate_add(x: torch.Tensor, gate: torch.Tensor, branch: torch.Tensor, m: torch.Tensor) -> torch.Tensor:
+    """m[t] += sigmoid(x[t] . gate) * branch[t]; x float32 [n, D], gate float32 [D], branch and m float32 [n, O]."""
+    _need(x, "x", torch.float32, (None, None))
+    n, D = x.shape
+    _need(gate, "gate", torch.float32, (D,))
+    _need(m, "m", torch.float32, (n, None))
+    _need(branch, "branch", torch.float32, tuple(m.shape))
+    _check(_fn("elementwise", "zk_gate_add")(_ptr(x), _ptr(gate), _ptr(branch), _ptr(m), n, D, m.shape[1], _stream()),
+           "gate_add")
+    return m
+
+
+# ------------------------------------------------------------------------------- convolution over time on a mixer's input
+
+def seqconv_max_taps() -> int:
+    return _constant("seqconv", "zk_seqconv_max_taps")
+
+
+def seqconv(x: torch.Tensor, state: torch.Tensor, taps: torch.Tensor, tok_seq, cu_q, seq_slot, n_seqs: int,
+            out_dtype: torch.dtype, residual: bool = True, single_token: bool = False) -> torch.Tensor:
+    """h_t = (x_t +) sum_j taps[j] * x_{t - (K-1) + j} per channel over each sequence's tokens, the
+    K-1 inputs before the step taken from `state` [slots, K-1, D], which then moves on to the step's
+    last inputs.  x float32 [n, D] packed; taps float32 [K, D]; h [n, D] in `out_dtype`."""
+    _need(x, "x", torch.float32, (None, None))
+    n, D = x.shape
+    _need(taps, "taps", torch.float32, (None, D))
+    K = taps.shape[0]
+    _need(state, "state", torch.float32, (None, K - 1, D))
+    for t, nm in ((tok_seq, "tok_seq"), (cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    h = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    _check(_fn("seqconv", "zk_seqconv_forward")(_ptr(x), _ptr(state), _ptr(taps), _ptr(tok_seq), _ptr(cu_q),
+                                                _ptr(seq_slot), _ptr(h), n, D, K, state.stride(0),
+                                                1 if residual else 0, 1 if single_token else 0, dtype_code(out_dtype),
+                                                _stream()), "seqconv")
+    if not single_token and K > 1:
+        _check(_fn("seqconv", "zk_seqconv_state_update")(_ptr(x), _ptr(state), _ptr(cu_q), _ptr(seq_slot), n_seqs, D, K,
+                                                         state.stride(0), _stream()), "seqconv state")
+    return h
+
+
+# ------------------------------------------------------------------------------- experts picked by a table
+
+def moe_table(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+              w_down: torch.Tensor, status: torch.Tensor, out: Optional[torch.Tensor] = None,
+              accumulate: bool = False) -> torch.Tensor:
+    """y[t] = (1/top) sum_k W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = table[tokens[t]][k].
+    x [n, D] run dtype; table int32 [vocab, top]; w_gate, w_up [E, F, D], w_down [E, D, F]; y float32 [n, D]."""
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
+    n, D = x.shape
+    _need(tokens, "tokens", torch.int32, (n,))
+    _need(table, "table", torch.int32, (None, None))
+    vocab, top = table.shape
+    _need(w_gate, "w_gate", x.dtype, (None, None, D))
+    E, F, _ = w_gate.shape
+    _need(w_up, "w_up", x.dtype, (E, F, D))
+    _need(w_down, "w_down", x.dtype, (E, D, F))
+    if out is None:
+        if accumulate:
+            raise KernelError("moe_table: accumulate needs an output tensor")
+        out = torch.empty((n, D), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, (n, D))
+    h = torch.empty((n, top, F), dtype=x.dtype, device=x.device)
+    _check(_fn("moe", "zk_moe_table")(_ptr(x), _ptr(tokens), _ptr(table), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(h),
+                                      _ptr(out), n, D, F, top, vocab, E, 1 if accumulate else 0, dtype_code(x.dtype),
+                                      _ptr(status), _stream()), "moe_table")
+    return out
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
@@ -616,6 +774,29 @@ def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_
     return q
 
 
+def qk_prepare_span(qkv, k_cache, v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot, page_table, n_heads: int, n_kv: int,
+                    head_dim: int, value_dim: int, eps: float, status, write_kv: bool = True) -> torch.Tensor:
+    """RMSNorm of q over all its heads at once (weight [H*hd], or None) and of k likewise ([Hkv*hd]),
+    no rotation; q out as [n, H*hd]; k and v (value_dim wide) written to their pages.  A row of qkv
+    holds [q | k | v], or q alone with write_kv False (the caches are then only needed for their sizes)."""
+    qd, kd, vd = n_heads * head_dim, n_kv * head_dim, n_kv * value_dim
+    _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, qd + (kd + vd if write_kv else 0)))
+    n = qkv.shape[0]
+    _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, None, head_dim))
+    _need(v_cache, "v_cache", qkv.dtype, (None, n_kv, None, value_dim))
+    if q_w is not None:
+        _need(q_w, "q norm weight", torch.float32, (qd,))
+    if k_w is not None:
+        _need(k_w, "k norm weight", torch.float32, (kd,))
+    _need(page_table, "page_table", torch.int32, (None, None))
+    q = torch.empty((n, qd), dtype=qkv.dtype, device=qkv.device)
+    _check(_fn("attention", "zk_qk_prepare_span")(
+        _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_w), _ptr(k_w), _ptr(tok_seq),
+        _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, value_dim,
+        eps, k_cache.shape[2], 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), _stream()), "qk_prepare_span")
+    return q
+
+
 def qk_normed(qkv, q_w, k_w, n_heads: int, n_kv: int, head_dim: int, eps: float, tok_pos, status) -> torch.Tensor:
     """Per-head RMSNorm of the q and k heads of qkv [n, (H + 2 Hkv) * hd] into a new tensor of
     the same shape (v copied); no rotation, no cache write."""
@@ -661,10 +842,13 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 
 @functools.lru_cache(maxsize=None)      # a pure function of sizes, asked for by every attention layer of every step
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                   single_token: bool, window: int = 0) -> tuple[str, int]:
+                   single_token: bool, window: int = 0, value_dim: Optional[int] = None,
+                   biased: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
-    ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile)."""
-    if dtype == torch.bfloat16 and n_heads % n_kv == 0:
+    ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
+    Values of another width than the keys, or a distance bias on the scores, go to the general kernel."""
+    plain = (value_dim is None or value_dim == head_dim) and not biased
+    if plain and dtype == torch.bfloat16 and n_heads % n_kv == 0:
         if (not single_token and window <= 0 and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
@@ -679,28 +863,42 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
 
 def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
               head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
-              single_token: bool = False, kind: Optional[str] = None) -> torch.Tensor:
+              single_token: bool = False, kind: Optional[str] = None, value_dim: Optional[int] = None,
+              bias: Optional[tuple] = None) -> torch.Tensor:
     """Causal grouped-query attention of a packed batch against the paged cache.  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
     bfloat16 kernels for that case are used when they take the sizes.  `kind` names the kernel as
     `attention_plan` chose it (the tile table must then have that plan's tokens per tile);
-    without it the general kernel or the single-token kernel runs."""
+    without it the general kernel or the single-token kernel runs.  `value_dim`: width of a value
+    row if it is not head_dim.  `bias` = (r1, r2), float32 [H] each: r1_h * ln(1 + r2_h * (i - j)) is taken
+    off the scaled score of query position i and key position j.  Both are the general kernel's."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
-    for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
-        _need(c, nm, q.dtype, (None, n_kv, None, head_dim))
+    vd = head_dim if value_dim is None else int(value_dim)
+    _need(k_cache, "k_cache", q.dtype, (None, n_kv, None, head_dim))
+    _need(v_cache, "v_cache", q.dtype, (None, n_kv, None, vd))
+    if bias is not None:
+        for b, nm in zip(bias, ("bias r1", "bias r2")):
+            _need(b, nm, torch.float32, (n_heads,))
+    if (vd != head_dim or bias is not None) and kind not in (None, "general"):
+        raise KernelError(f"attention: the '{kind}' kernel takes neither a value width of its own nor a distance bias")
     page_size = k_cache.shape[2]
     if n_heads % n_kv:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv} KV heads")
     if head_dim > attn_max_head_dim():
         raise KernelError(f"attention: head_dim {head_dim} exceeds {attn_max_head_dim()}")
+    if vd > attn_max_head_dim():
+        raise KernelError(f"attention: value_dim {vd} exceeds {attn_max_head_dim()}")
     bq, gc = attn_tile_shape(n_heads, n_kv)
     n_tiles = tile_seq.numel()
-    out = torch.empty_like(q)
+    out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
+    general_only = vd != head_dim or bias is not None
+    if general_only:
+        single_token = False        # the general kernel runs single tokens as tiles of one query
     part_o = part_ml = None
     if num_splits > 1:
-        part_o = torch.empty((num_splits, n * n_heads, head_dim), dtype=torch.float32, device=q.device)
+        part_o = torch.empty((num_splits, n * n_heads, vd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
     if kind == "prompt_tc5":
         if (q.dtype != torch.bfloat16 or window > 0 or not k_cache.is_contiguous() or not v_cache.is_contiguous()
@@ -747,10 +945,11 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     _check(_fn("attention", "zk_attn_fwd")(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
-        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), _stream()),
+        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd,
+        _ptr(bias[0]) if bias else None, _ptr(bias[1]) if bias else None, _stream()),
         "attention")
     if num_splits > 1:
-        _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
+        _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,
                                                  num_splits, dtype_code(q.dtype), _stream()), "attention merge")
     return out
 

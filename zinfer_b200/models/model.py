@@ -28,9 +28,12 @@ class LayerCall:
 class Model:
     def __init__(self, config: ModelConfig, embedding: TokenEmbedding, layers: Sequence[Block],
                  final_norm: Norm, head: LMHead, schedule: Optional[Sequence[LayerCall]] = None,
-                 ignorable_weights: Sequence[str] = ()):
+                 ignorable_weights: Sequence[str] = (), depth_mix=None):
+        """depth_mix: a `parts.depth.DepthAverage` (or None): after every schedule entry the rows that go
+        on are a weighted sum of all results so far instead of the entry's result alone."""
         self.config = config
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
+        self.depth_mix = depth_mix
         self.schedule = list(schedule) if schedule is not None else [LayerCall(i) for i in range(len(self.layers))]
         self.ignorable_weights = tuple(ignorable_weights)
         self.dtype: Optional[torch.dtype] = None
@@ -45,7 +48,8 @@ class Model:
     def all_parts(self) -> list[Part]:
         out: list[Part] = []
         seen: set[int] = set()
-        for top in (self.embedding, *self.layers, self.final_norm, self.head):
+        tops = (self.embedding, *self.layers, self.final_norm, self.head)
+        for top in tops if self.depth_mix is None else (*tops, self.depth_mix):
             for p in walk_parts(top):
                 if id(p) not in seen:
                     seen.add(id(p))
@@ -82,14 +86,24 @@ class Model:
         listed in `want_rows` (row indices into the packed tokens), of every row with `want_all`
         (written into `out` if given), or None when none is wanted.  Only wanted rows meet the
         final norm and the head (src/model.zig:2482-2490)."""
-        x = self.embedding.forward(ctx, ctx.tokens)
+        mix = self.depth_mix
+        if mix is not None:
+            planes = mix.planes(ctx, len(calls), self.embedding.dim)
+            self.embedding.forward(ctx, ctx.tokens, out=planes[0])
+            x = mix.first_input(planes)
+        else:
+            x = self.embedding.forward(ctx, ctx.tokens)
         carried = None      # what a block's last contraction prepared for the norm that reads x next
         for i, call_ctx in enumerate(calls):
-            if i + 1 < len(calls):
+            if mix is not None:
+                next_norm = None        # the rows the next norm reads are not the rows this block sums into
+            elif i + 1 < len(calls):
                 next_norm = self.layers[calls[i + 1].layer].entry_norm()
             else:
                 next_norm = self.final_norm if want_all else None
             carried = self.layers[call_ctx.layer].forward_chained(ctx, call_ctx, x, carried, next_norm)
+            if mix is not None:
+                x = mix.after(planes, i)
         if want_all:
             return self.head.forward(ctx, normed_for(self.head, self.final_norm, ctx, x, carried), out=out)
         if want_rows is None or want_rows.numel() == 0:

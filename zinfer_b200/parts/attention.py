@@ -8,7 +8,14 @@ written to the cache at the tokens' absolute positions; every query then attends
 (src/model.zig:1362-1363); the output projection adds into the residual stream
 (src/model.zig:1988-1990).  Scores are scaled by 1/sqrt(head_dim) (src/model.zig:465).
 
-A call that reads another call's cache (`call.writes_kv` False) computes only its queries.
+A call that reads another call's cache (`call.writes_kv` False) computes only its queries; a
+mixer built with `own_kv=False` has no key and value weights at all and can only run in such a call.
+
+Options that other designs use: `value_dim` (values of another width than keys), `qk_norm_span`
+"all" (the q norm runs over all heads of a token at once with a weight of that width, likewise k;
+"head" is the per-head norm with a weight of head_dim), `distance_bias` = (name of r1, name of r2),
+two numbers per query head: r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query
+position i and key position j, in float32, before the softmax.
 
 How the kernels are launched is decided here, not by the engine: the table of query tiles of a
 step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
@@ -79,11 +86,24 @@ class GqaAttention(Mixer):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, q_name: str, k_name: str,
                  v_name: str, out_name: str, q_norm_name: Optional[str] = None, k_norm_name: Optional[str] = None,
                  norm_eps: float = 1e-5, position: Optional[PositionEncoding] = None, window: int = 0,
-                 scale: Optional[float] = None, split_keys: int = 0):
+                 scale: Optional[float] = None, split_keys: int = 0, value_dim: Optional[int] = None,
+                 qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True):
         """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
         step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} KV heads")    # src/model.zig:487
+        if qk_norm_span not in ("head", "all"):
+            raise ValueError(f"qk_norm_span {qk_norm_span!r}: 'head' or 'all'")
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        self.qk_norm_span, self.distance_bias, self.own_kv = qk_norm_span, distance_bias, bool(own_kv)
+        # the kernel that prepares q and k over the whole projection has no rotation
+        self.span_prepare = qk_norm_span == "all" or self.value_dim != head_dim or not own_kv
+        if self.span_prepare and position is not None:
+            raise ValueError("attention: a position encoding goes with per-head norms, equal key and value widths "
+                             "and key/value weights of the mixer's own")
+        if self.span_prepare and qk_norm_span == "head" and (q_norm_name or k_norm_name):
+            raise ValueError("attention: per-head norms go with equal key and value widths and own key/value weights")
+        self.bias_r1 = self.bias_r2 = None
         self.split_keys = int(split_keys)
         self._sm_count = 0
         self.hidden, self.n_heads, self.n_kv, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
@@ -101,32 +121,54 @@ class GqaAttention(Mixer):
     def kv_dim(self):
         return self.n_kv * self.head_dim
 
+    @property
+    def v_dim(self):
+        return self.n_kv * self.value_dim
+
+    @property
+    def out_dim(self):
+        return self.n_heads * self.value_dim
+
     def parts(self):
         return [self.position] if self.position is not None else []
 
     def weight_specs(self):
         specs = [WeightSpec(self.q_name, (self.q_dim, self.hidden)),
-                 WeightSpec(self.k_name, (self.kv_dim, self.hidden)),
-                 WeightSpec(self.v_name, (self.kv_dim, self.hidden)),
-                 WeightSpec(self.out_name, (self.hidden, self.q_dim))]
-        for n in (self.q_norm_name, self.k_norm_name):
-            if n is not None:
-                specs.append(WeightSpec(n, (self.head_dim,), role="vector", init="norm"))
+                 WeightSpec(self.out_name, (self.hidden, self.out_dim))]
+        if self.own_kv:
+            specs += [WeightSpec(self.k_name, (self.kv_dim, self.hidden)),
+                      WeightSpec(self.v_name, (self.v_dim, self.hidden))]
+        whole = self.qk_norm_span == "all"
+        if self.q_norm_name is not None:
+            specs.append(WeightSpec(self.q_norm_name, (self.q_dim if whole else self.head_dim,), role="vector", init="norm"))
+        if self.k_norm_name is not None and self.own_kv:
+            specs.append(WeightSpec(self.k_norm_name, (self.kv_dim if whole else self.head_dim,), role="vector", init="norm"))
+        if self.distance_bias is not None:
+            specs += [WeightSpec(n, (self.n_heads,), role="vector", init="abs_normal") for n in self.distance_bias]
         return specs
 
     def load(self, weights, dtype, device):
-        self.w_qkv = torch.cat([weights[self.q_name], weights[self.k_name], weights[self.v_name]], dim=0).contiguous()
+        if self.own_kv:
+            self.w_qkv = torch.cat([weights[self.q_name], weights[self.k_name], weights[self.v_name]], dim=0).contiguous()
+        else:
+            self.w_qkv = weights[self.q_name]
         self.w_out = weights[self.out_name]
         self.q_norm = weights[self.q_norm_name] if self.q_norm_name else None
-        self.k_norm = weights[self.k_norm_name] if self.k_norm_name else None
+        self.k_norm = weights[self.k_norm_name] if self.k_norm_name and self.own_kv else None
+        if self.distance_bias is not None:
+            self.bias_r1, self.bias_r2 = (weights[n] for n in self.distance_bias)
         self._sm_count = kernels.sm_count(device) if torch.device(device).type == "cuda" else 0
 
     def kv_request(self):
-        return KVRequest(self.n_kv, self.head_dim, self.window)
+        return KVRequest(self.n_kv, self.head_dim, self.window,
+                         None if self.value_dim == self.head_dim else self.value_dim)
 
     def check(self, dtype, page_size):
         most = kernels.attn_max_head_dim()
-        if self.head_dim % 2 or self.head_dim > most:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
+        if self.span_prepare:
+            if not 0 < self.head_dim <= most or not 0 < self.value_dim <= most:
+                raise ValueError(f"attention: head_dim {self.head_dim} and value_dim {self.value_dim} must be at most {most}")
+        elif self.head_dim % 2 or self.head_dim > most:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
             raise ValueError(f"attention: head_dim {self.head_dim} must be even and at most {most}")
         if self.split_keys < 0 or self.split_keys % CHUNK_ALIGN:
             raise ValueError(f"attention: split_keys {self.split_keys} must be a multiple of {CHUNK_ALIGN}")
@@ -139,12 +181,19 @@ class GqaAttention(Mixer):
 
     def forward(self, ctx, call, xn, out, accumulate):
         kv = call.kv
-        qkv = linear(xn, self.w_qkv)
+        if not self.own_kv and call.writes_kv:
+            raise ValueError("attention: a mixer without key and value weights must read another call's cache")
+        # a call that reads another call's cache needs its queries only (the stacked rows start with q)
+        w_qkv = self.w_qkv[:self.q_dim] if self.span_prepare and self.own_kv and not call.writes_kv else self.w_qkv
+        qkv = linear(xn, w_qkv)
         rot = self.position.rotary() if self.position is not None else None
         fused = self.position is None or rot is not None
         common = dict(tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot, page_table=kv.page_table,
                       n_heads=self.n_heads, n_kv=self.n_kv, head_dim=self.head_dim, eps=self.eps, status=ctx.status)
-        if fused:
+        if self.span_prepare:
+            q = kernels.qk_prepare_span(qkv, kv.k, kv.v, self.q_norm, self.k_norm, value_dim=self.value_dim,
+                                        write_kv=call.writes_kv, **common)
+        elif fused:
             q = kernels.qk_prepare(qkv, kv.k, kv.v, self.q_norm, self.k_norm, rot.inv_freq if rot else None,
                                    n_rot=rot.n_rot if rot else 0, interleaved=rot.interleaved if rot else False,
                                    write_kv=call.writes_kv, **common)
@@ -157,13 +206,16 @@ class GqaAttention(Mixer):
             q = kernels.qk_prepare(normed, kv.k, kv.v, None, None, None, n_rot=0, interleaved=False,
                                    write_kv=call.writes_kv, **common)
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
-                                                   ctx.is_decode, self.window)
+                                                   ctx.is_decode, self.window, self.value_dim,
+                                                   self.distance_bias is not None)
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
                                 kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
-                                num_splits, split_keys, single_token=ctx.is_decode, kind=kind)
+                                num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
+                                value_dim=self.value_dim,
+                                bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 

@@ -47,7 +47,8 @@ class WeightSpec:
     role: "matrix" is kept in the run dtype (bfloat16, or float32 in the 32-bit path);
     "vector" (norm weights, conv taps, biases) is kept in float32, which holds a stored
     bfloat16 or float32 value exactly; "table" is an integer table kept as int32.
-    init: how the random-weights mode fills it ("normal", "one_plus_normal", "zeros").
+    init: how the random-weights mode fills it ("normal", "one_plus_normal", "abs_normal" = |normal|,
+    "zeros"; a table gets rows of distinct integers in [0, bound)).
     alt_shapes: other stored shapes with the same element order (e.g. [D, 1, K] for [D, K]);
     the random-weights mode stores the first of them if there is one.
     """
@@ -58,6 +59,7 @@ class WeightSpec:
     optional: bool = False
     init: str = "normal"
     alt_shapes: tuple[tuple[int, ...], ...] = ()
+    bound: int = 0
 
 
 @dataclass(frozen=True)

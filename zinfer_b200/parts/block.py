@@ -57,4 +57,40 @@ def ahead_for(producer, norm, ctx, x):
     return ahead(ctx, x) if ahead is not None else None
 
 
+class SublayerNormBlock(Block):
+    """x += norm1(Mixer(x)); x += norm2(FFN(x)): the norms sit on the sublayers' OUTPUTS and the
+    sublayers read the residual rows as they are.  Either sublayer may be absent (`ffn` None).
+
+    A part that sets `takes_residual_rows = True` is handed the float32 rows themselves (it may
+    want them in 32-bit: a convolution with state, a gate); any other part gets them in the run
+    dtype.  The part writes its result into a float32 buffer of the rows' shape (`accumulate`
+    False); `Norm.add_normed` then sums its norm into the rows."""
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward | None = None, ffn_norm: Norm | None = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        for n in (mixer_norm, ffn_norm):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError(f"{type(n).__name__} cannot sum a normalised sublayer output into the rows")
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    @staticmethod
+    def _input(part, ctx, x):
+        from .. import kernels
+        return x if getattr(part, "takes_residual_rows", False) else kernels.cast_rows(x, ctx.dtype)
+
+    def forward(self, ctx, call, x):
+        import torch
+        m = torch.empty_like(x)
+        self.mixer.forward(ctx, call, self._input(self.mixer, ctx, x), m, False)
+        self.mixer_norm.add_normed(ctx, m, x)
+        if self.ffn is not None:
+            self.ffn.forward(ctx, self._input(self.ffn, ctx, x), m, False)
+            self.ffn_norm.add_normed(ctx, m, x)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("sublayer_norm", SublayerNormBlock)

@@ -57,4 +57,29 @@ class SwiGLU(FeedForward):
         linear(h, self.w_down, out=out, accumulate=accumulate)
 
 
+class ActMlp(FeedForward):
+    """Ungated feed-forward: out (+)= act(xn W_up^T) W_down^T, act one of `kernels.ACTIVATIONS`
+    ("gelu" is the exact erf form), evaluated in float32."""
+
+    sums_through_linear = True
+
+    def __init__(self, hidden: int, ffn_dim: int, up_name: str, down_name: str, act: str = "gelu"):
+        if act not in kernels.ACTIVATIONS:
+            raise ValueError(f"activation {act!r}; known: {sorted(kernels.ACTIVATIONS)}")
+        self.hidden, self.ffn_dim, self.up_name, self.down_name, self.act = hidden, ffn_dim, up_name, down_name, act
+        self.w_up = self.w_down = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.up_name, (self.ffn_dim, self.hidden)),
+                WeightSpec(self.down_name, (self.hidden, self.ffn_dim))]
+
+    def load(self, weights, dtype, device):
+        self.w_up, self.w_down = weights[self.up_name], weights[self.down_name]
+
+    def forward(self, ctx, xn, out, accumulate):
+        u = linear(xn, self.w_up)
+        linear(kernels.activation(u, self.act, out=u), self.w_down, out=out, accumulate=accumulate)
+
+
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("act_mlp", ActMlp)

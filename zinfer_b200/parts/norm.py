@@ -25,6 +25,11 @@ class RMSNorm(Norm):
     def forward(self, ctx, x, rows=None):
         return kernels.rmsnorm(x, self.weight, self.eps, ctx.dtype, rows)
 
+    def add_normed(self, ctx, m, x):
+        """x += norm(m), row by row in float32: the form a block needs that normalises what a sublayer
+        RETURNS instead of what it reads."""
+        return kernels.rmsnorm_add(m, self.weight, self.eps, x)
+
     def pending(self, ctx, x, prepared=None):
         """All rows, not yet normalised: `linear` and the fused kernels resolve a `NormedRows`.
         `prepared` is what `ahead` returned for these rows, after the contraction that got it ran."""

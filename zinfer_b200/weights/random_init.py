@@ -26,6 +26,8 @@ from .safetensors_io import write_safetensors
 def _tensor(spec: WeightSpec, seed: int, std: float, norm_init: str, storage_dtype: torch.dtype) -> torch.Tensor:
     rng = np.random.Generator(np.random.Philox(key=[seed & 0xFFFFFFFFFFFFFFFF, zlib.crc32(spec.name.encode())]))
     count = int(np.prod(spec.shape))
+    if spec.role == "table":
+        return _table(spec, rng)
     init = spec.init
     if init == "norm":
         init = norm_init
@@ -35,10 +37,21 @@ def _tensor(spec: WeightSpec, seed: int, std: float, norm_init: str, storage_dty
         vals = rng.standard_normal(count, dtype=np.float32) * np.float32(std)
         if init == "one_plus_normal":
             vals += np.float32(1.0)
+        elif init == "abs_normal":
+            vals = np.abs(vals)
         elif init != "normal":
             raise ValueError(f"tensor '{spec.name}': unknown init {spec.init!r}")
     shape = spec.alt_shapes[0] if spec.alt_shapes else spec.shape
     return torch.from_numpy(vals).reshape(shape).to(storage_dtype)
+
+
+def _table(spec: WeightSpec, rng) -> torch.Tensor:
+    """An integer table whose rows hold distinct values of [0, bound)."""
+    rows, width = int(np.prod(spec.shape[:-1])), spec.shape[-1]
+    if spec.bound < width:
+        raise ValueError(f"tensor '{spec.name}': rows of {width} distinct entries need a bound of at least {width}")
+    order = np.argsort(rng.random((rows, spec.bound)), axis=1)[:, :width]
+    return torch.from_numpy(order.astype(np.int32)).reshape(spec.shape)
 
 
 def random_tensors(model, seed: int, std: float = 0.02, norm_init: str = "one_plus_normal",
@@ -46,8 +59,6 @@ def random_tensors(model, seed: int, std: float = 0.02, norm_init: str = "one_pl
     for name, spec in model.weight_specs().items():
         if spec.init == "skip":
             continue
-        if spec.role == "table":
-            raise ValueError(f"tensor '{name}': integer tables have no random fill")
         yield spec, _tensor(spec, seed, std, norm_init, storage_dtype)
 
 
@@ -63,14 +74,17 @@ def random_tensors_on_device(model, seed: int, std: float, norm_init: str, stora
     for name, spec in model.weight_specs().items():
         if spec.init == "skip":
             continue
-        if spec.role == "table":
-            raise ValueError(f"tensor '{name}': integer tables have no random fill")
+        if spec.role == "table":      # small, and integer: drawn on the host
+            yield spec, _tensor(spec, seed, std, norm_init, storage_dtype).to(device)
+            continue
         init = norm_init if spec.init == "norm" else spec.init
         t = torch.empty(spec.alt_shapes[0] if spec.alt_shapes else spec.shape, dtype=storage_dtype, device=device)
         if init == "zeros":
             t.zero_()
-        elif init in ("normal", "one_plus_normal"):
+        elif init in ("normal", "one_plus_normal", "abs_normal"):
             kernels.fill_normal(t, (seed << 32) ^ zlib.crc32(name.encode()), 1.0 if init == "one_plus_normal" else 0.0, std)
+            if init == "abs_normal":
+                t.abs_()
         else:
             raise ValueError(f"tensor '{name}': unknown init {spec.init!r}")
         yield spec, t
