@@ -141,7 +141,9 @@ class CacheManager:
         self.max_slots, self.max_seq_len, self.page_size = max_slots, max_seq_len, page_size
         self.dtype, self.device = dtype, device
         self.num_pages = -(-max_tokens // page_size)
-        self.max_pages_per_seq = min(-(-max_seq_len // page_size), self.num_pages)
+        # a page-table row covers the longest sequence, not the pool: a windowed group gives pages back while
+        # the sequence grows, so a sequence may be longer than all the pages there are
+        self.max_pages_per_seq = -(-max_seq_len // page_size)
         self.lengths = np.zeros(max_slots, dtype=np.int64)
         self.active = np.zeros(max_slots, dtype=bool)
         self.free_slot_list = list(range(max_slots - 1, -1, -1))
