@@ -44,7 +44,7 @@ def engine_for(zoo, name, dtype, **kw):
     import zinfer_b200 as z
     model = z.load(zoo[name][2], dtype=dtype)
     kw.setdefault("max_batch", 4)
-    kw.setdefault("page_size", 16)
+    kw.setdefault("page_size", 64 if name == "pc" else 16)      # pc: the page size the tensor-core attention kernels take
     return z.Engine(model, **kw)
 
 

@@ -24,8 +24,9 @@ def k():
     return kernels
 
 
-def context(k, dtype, cache, slots, token_lists):
-    """A step context for `token_lists` continuing the sequences in `slots` of `cache`."""
+def context(k, dtype, cache, slots, token_lists, host=True):
+    """A step context for `token_lists` continuing the sequences in `slots` of `cache`; `host`: the context
+    also carries the ids on the host, as a prompt step's does."""
     from zinfer_b200.engine.context import StepContext, pack_batch
     lens = [len(t) for t in token_lists]
     starts = [int(cache.lengths[s]) for s in slots]
@@ -33,7 +34,8 @@ def context(k, dtype, cache, slots, token_lists):
     cache.sync()
     buf = torch.from_numpy(pack_batch(slots, starts, token_lists)).cuda()
     return StepContext(dtype, torch.device("cuda"), k.status_word("cuda"), buf, sum(lens), len(slots), lens,
-                       max(s + n for s, n in zip(starts, lens)))
+                       max(s + n for s, n in zip(starts, lens)),
+                       host_tokens=np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists]) if host else None)
 
 
 # ------------------------------------------------------------------------------- row kernels
@@ -199,6 +201,9 @@ def plain_mixer(x, t, H, G, d, vd, scale, window, kv=None):
     (96, 4, 2, 32, 16, 0.2, 33, 32),        # values narrower than keys, a window longer than a page
     (128, 8, 2, 64, 64, 0.125, 16, 16),     # the widths the tensor-core kernels take; a window of one page
     (72, 6, 2, 24, 40, 0.15, 1, 16),        # a window of ONE token: every query sees itself only
+    (128, 8, 2, 64, 64, 0.125, 40, 64),     # pages of 64: in bfloat16 the tensor-core kernels run
+    (96, 2, 1, 128, 128, 0.1, 70, 64),      # heads of 128, a window over a page border
+    (64, 16, 1, 64, 64, 0.2, 0, 64),        # sixteen heads on one key/value head, no window
 ])
 def test_log_distance_attention_part(k, dtype, D, H, G, d, vd, scale, window, page):
     t = attention_tensors(D, H, G, d, vd, dtype, 40)
@@ -212,17 +217,19 @@ def test_log_distance_attention_part(k, dtype, D, H, G, d, vd, scale, window, pa
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window,page,prompt", [(0, 16, 150), (0, 64, 40), (48, 16, 120), (64, 64, 70), (37, 32, 3)])
-def test_one_key_decides(k, dtype, window, page, prompt):
+@pytest.mark.parametrize("d", [16, 64])      # heads of 64 with pages of 64: the tensor-core kernels in bfloat16
+@pytest.mark.parametrize("window,page,prompt", [(0, 16, 150), (0, 64, 40), (48, 16, 120), (64, 64, 70), (37, 32, 3),
+                                                (65, 64, 130), (128, 64, 2)])
+def test_one_key_decides(k, dtype, window, page, prompt, d):
     """Rows are made so that a few MARKED tokens carry the key direction of the queries that follow, each
     with a value of its own; everything else scores ten lower.  Marked: the first token, the tokens on both
     sides of every page border, and for each probing query the tokens just inside (distance window - 1) and
     just outside (distance window) its window.  A kernel that misses a marked key, sees one it must not, or
     reads another page or row gives another value: an error of order one."""
-    D, H, G, d, vd, scale, T = 64, 2, 1, 16, 16, 2.0, 200
+    D, H, G, vd, scale, T = 64, 2, 1, d, 32.0 / d, 200
     t = attention_tensors(D, H, G, d, vd, dtype, 60, split=True)
     for h in range(H):                  # every head's query projection is the key projection, norm weights are 1:
-        t["q"][h * d:(h + 1) * d] = t["k"]      # a query that follows key_dir scores 2 d = 32 on a marked key
+        t["q"][h * d:(h + 1) * d] = t["k"]      # a query that follows key_dir scores scale * d = 32 on a marked key
     t["qn"][:] = 1.0
     t["kn"][:] = 1.0
     t["r1"][:] = 0.25
@@ -322,17 +329,26 @@ def test_table_routed_experts(k, dtype, D, F, E, top, shared, rows):
     x = rnd((rows, D), 300, dtype)
     out = torch.full((rows, D), 9.0, device="cuda")
     moe.forward(ctx, x.cuda(), out, False)
+    from zinfer_b200.parts.moe import GROUPED_MIN_TOKENS
+    assert (rows >= GROUPED_MIN_TOKENS) == (rows == 200), "the test means to run both ways"
     f = lambda n: t[n].numpy().astype(np.float64)
     ref = P.table_experts(x.numpy().astype(np.float64), toks, t["table"].numpy(), [(f(f"e{e}.g"), f(f"e{e}.u"), f(f"e{e}.d")) for e in range(E)],
                           (f("s.g"), f("s.u"), f("s.d")) if shared else None, f("s.sg").reshape(-1) if shared else None)
     close(out, ref, dtype, "experts")
     assert int(ctx.status.item()) == 0
+    if rows >= GROUPED_MIN_TOKENS:       # the same step without the ids on the host: the streaming kernels, added into `out`
+        cache2 = CacheManager([CallCacheSpec()], 1, 256, 256, 16, dtype, "cuda")
+        ctx2 = context(k, dtype, cache2, cache2.alloc_slots(1), [toks], host=False)
+        base = torch.full((rows, D), 0.25, device="cuda")
+        both = base.clone()
+        moe.forward(ctx2, x.cuda(), both, True)
+        close(both - base, ref, dtype, "experts, streamed")
     # a row's result does not depend on the rows beside it
     one = torch.empty((1, D), device="cuda")
     cache1 = CacheManager([CallCacheSpec()], 1, 256, 256, 16, dtype, "cuda")
     ctx1 = context(k, dtype, cache1, cache1.alloc_slots(1), [toks[-1:]])
     moe.forward(ctx1, x[-1:].cuda(), one, False)
-    if dtype == torch.float32:
+    if dtype == torch.float32 and rows < GROUPED_MIN_TOKENS:       # the same kernels ran: the same bits
         assert torch.equal(one[0], out[-1])
     else:
         close(one, ref[-1:], dtype, "alone")

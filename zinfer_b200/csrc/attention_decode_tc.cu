@@ -71,7 +71,10 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
                           bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                           const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                           const int* __restrict__ page_table, int pt_stride, int n_seqs, int H, int Hkv, int page_size,
-                          int window, float scale, int num_splits, int split_keys) {
+                          int window, float scale, int num_splits, int split_keys, const float* __restrict__ bias_r1,
+                          const float* __restrict__ bias_r2) {
+  // bias_r1, bias_r2 [H] (both or neither): r1_h * ln(1 + r2_h * distance) is taken off the scaled score of the
+  // key `distance` tokens behind the query, in float32 (here on base 2, like the scores).
   constexpr int KS = HD / 16;               // k steps of Q K^T
   constexpr int CH = HD / 8;                // 16-byte chunks per row
   constexpr int TILE_BYTES = DT_TK * HD * 2;
@@ -154,6 +157,16 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   // The softmax runs on base 2: scores are scaled by scale * log2(e) and the exponentials are ex2.approx
   // (one instruction where expf is eight); the maxima go back to base e when they leave the loop.
   const float scale2 = scale * 1.4426950408889634f;
+  const bool biased = bias_r1 != nullptr;
+  float r1_2[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f};     // row g = head g of the group, row g + 8 = head g + 8
+  if (biased) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int head = kvh * G + min(g + 8 * h, G - 1);
+      r1_2[h] = bias_r1[head] * 1.4426950408889634f;
+      r2[h] = bias_r2[head];
+    }
+  }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[HD / 8][4];
 #pragma unroll
@@ -200,12 +213,14 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
+        const int kp = kb + 8 * j + 2 * c + (i & 1);
+        float sc = s[j][i] * scale2;
+        if (biased) sc -= r1_2[i >> 1] * log1pf(r2[i >> 1] * (float)max(L - 1 - kp, 0));
         if (edge_tile) {
-          const int kp = kb + 8 * j + 2 * c + (i & 1);
           const bool vis = kp >= c0 && kp < c1;
-          s[j][i] = vis ? s[j][i] * scale2 : -INFINITY;
+          s[j][i] = vis ? sc : -INFINITY;
         } else {
-          s[j][i] *= scale2;
+          s[j][i] = sc;
         }
         m_new[i >> 1] = fmaxf(m_new[i >> 1], s[j][i]);
       }
@@ -309,7 +324,8 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
 template <int HD, int NST>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int Hkv,
-           int page_size, int window, float scale, int num_splits, int split_keys, cudaStream_t stream) {
+           int page_size, int window, float scale, int num_splits, int split_keys, const float* r1, const float* r2,
+           cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<HD, NST>;
   const size_t smem = 2 * NST * (size_t)DT_TK * HD * 2;
   static_assert(2 * NST * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
@@ -320,7 +336,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   dim3 grid(n_seqs, Hkv, num_splits);
   return zk_launch_dependent(kern, grid, dim3(DT_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, Hkv,
-                                              page_size, window, scale, num_splits, split_keys);
+                                              page_size, window, scale, num_splits, split_keys, r1, r2);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -341,9 +357,10 @@ int zk_attn_decode_tc_takes(int H, int Hkv, int hd, int page_size) {
 int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                       const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H,
                       int Hkv, int hd, int page_size, int window, float scale, int num_splits, int split_keys,
-                      cudaStream_t stream) {
+                      const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (!zk_attn_decode_tc_takes(H, Hkv, hd, page_size) || num_splits < 1) return ZK_EINVAL;
+  if ((bias_r1 == nullptr) != (bias_r2 == nullptr)) return ZK_EINVAL;
   if (num_splits > 1 && (split_keys <= 0 || split_keys % DT_TK || !part_o || !part_ml)) return ZK_EINVAL;
   // Tile buffers (head_dim 64): a block whose chunk is at most four tiles asks for all of them at once;
   // longer chunks are double-buffered, because more blocks on an SM hide more latency than a deeper
@@ -354,12 +371,12 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
   if (hd == 64 && short_chunks)
     return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
   if (hd == 64)
     return launch<64, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
   return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                     Hkv, page_size, window, scale, num_splits, split_keys, stream);
+                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
 }
 
 }  // extern "C"

@@ -60,7 +60,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
                         bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
                         const int* __restrict__ cu_q, const int* __restrict__ seq_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
-                        int Hkv, int page_size, int window, float scale) {
+                        int Hkv, int page_size, int window, float scale, const float* __restrict__ bias_r1,
+                        const float* __restrict__ bias_r2) {
+  // bias_r1, bias_r2 [H] (both or neither): r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of
+  // query position i and key position j, in float32, before the softmax.
   constexpr int BQ = PF_ROWS / GP;          // tokens per block
   constexpr int KS = HD / 16;               // k steps of Q K^T
   constexpr int CH = HD / 8;                // 16-byte chunks per row
@@ -93,6 +96,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
     row_head[h] = kvh * G + chunk * GP + hl;
     row_hi[h] = start + q0 + tq + 1;
     row_lo[h] = (window > 0 && row_hi[h] > window) ? row_hi[h] - window : 0;
+  }
+  const bool biased = bias_r1 != nullptr;
+  float r1[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f};
+  if (biased) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      r1[h] = bias_r1[row_head[h]];
+      r2[h] = bias_r2[row_head[h]];
+    }
   }
 
   // Q fragments straight from global memory: a0a1 = Q[row g][2c, 2c+1], a2a3 = row g+8, a4a5 / a6a7 = +8 in k
@@ -177,7 +189,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
         const int h = i >> 1;
         const int kp = kb + 8 * j + 2 * c + (i & 1);
         const bool vis = row_ok[h] && kp >= row_lo[h] && kp < row_hi[h];
-        s[j][i] = vis ? s[j][i] * scale : -INFINITY;
+        float sc = s[j][i] * scale;
+        if (biased && vis) sc -= r1[h] * log1pf(r2[h] * (float)(row_hi[h] - 1 - kp));
+        s[j][i] = vis ? sc : -INFINITY;
         m_new[h] = fmaxf(m_new[h], s[j][i]);
       }
     float alpha[2], row_sum[2] = {0.f, 0.f};
@@ -245,7 +259,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
 template <int HD, int GP>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_q0,
            const int* cu_q, const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_tiles,
-           int H, int Hkv, int page_size, int window, float scale, cudaStream_t stream) {
+           int H, int Hkv, int page_size, int window, float scale, const float* r1, const float* r2,
+           cudaStream_t stream) {
   auto kern = attn_prefill_kernel<HD, GP>;
   const size_t smem = 4 * (size_t)PF_TK * HD * 2;
   if (smem > 48 * 1024) {
@@ -255,7 +270,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
   dim3 grid(n_tiles, Hkv * ((H / Hkv) / GP));
   kern<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, pt_stride, H,
-                                              Hkv, page_size, window, scale);
+                                              Hkv, page_size, window, scale, r1, r2);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -281,14 +296,14 @@ int zk_attn_prefill_tile_tokens(int H, int Hkv) { return PF_ROWS / packed_heads(
 int zk_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                     const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                     const int* page_table, int pt_stride, int n_tiles, int H, int Hkv, int hd, int page_size,
-                    int window, float scale, cudaStream_t stream) {
+                    int window, float scale, const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (!zk_attn_prefill_takes(H, Hkv, hd, page_size)) return ZK_EINVAL;
+  if (!zk_attn_prefill_takes(H, Hkv, hd, page_size) || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
   const int gp = packed_heads(H / Hkv);
 #define ZK_PF(HDV, GPV)                                                                                          \
   if (hd == HDV && gp == GPV)                                                                                    \
     return launch<HDV, GPV>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,  \
-                            pt_stride, n_tiles, H, Hkv, page_size, window, scale, stream);
+                            pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, stream);
   ZK_PF(64, 1) ZK_PF(64, 2) ZK_PF(64, 4) ZK_PF(64, 8)
   ZK_PF(128, 1) ZK_PF(128, 2) ZK_PF(128, 4) ZK_PF(128, 8)
 #undef ZK_PF

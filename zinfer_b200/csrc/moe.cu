@@ -5,7 +5,14 @@
 // hidden units; a warp owns a hidden unit at a time, its lanes walk the input row, sums in float32,
 // silu in float32.  (2) down: one block per token and slice of the outputs; the `top` experts are
 // added in the order of k, so a token's result does not depend on the rest of the batch.
-// Weights are stacked [experts, rows, cols] in the run dtype; x and h are the run dtype, y float32.
+// Weights are stacked in the run dtype: gate and up as ONE tensor [experts, 2F, D] whose rows are
+// [gate (F) | up (F)] (il = 0) or groups of il gate rows followed by their il up rows (il > 0, the layout
+// the contraction kernels with an activation epilogue want), down as [experts, D, F]; x and h are the run
+// dtype, y float32.
+//
+// For steps of many tokens there are two helper kernels instead: rows gathered in the order of their
+// experts (so that each expert's rows are one contiguous matrix for a tensor-core contraction) and the
+// weighted sum of a token's `top` result rows, added in the order of k.
 #include "common.cuh"
 
 #define MOE_WARPS 8
@@ -63,7 +70,7 @@ __device__ __forceinline__ int moe_expert(const int* __restrict__ tokens, const 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ table,
-                       const T* __restrict__ w_gate, const T* __restrict__ w_up, T* __restrict__ h, int D, int F,
+                       const T* __restrict__ w_gu, int il, T* __restrict__ h, int D, int F,
                        int top, int vocab, int n_experts, int units_per_block, int* status) {
   extern __shared__ float xs[];     // [D]
   zk_let_next_start();
@@ -73,12 +80,13 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
   for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * D + d]);
   __syncthreads();
-  const T* wg = w_gate + (size_t)e * F * D;
-  const T* wu = w_up + (size_t)e * F * D;
+  const T* w = w_gu + (size_t)e * 2 * F * D;
   const int f0 = blockIdx.y * units_per_block, f1 = min(F, f0 + units_per_block);
   for (int f = f0 + warp; f < f1; f += MOE_WARPS) {
-    const float g = row_dot<T, VEC>(wg + (size_t)f * D, xs, D, lane);
-    const float u = row_dot<T, VEC>(wu + (size_t)f * D, xs, D, lane);
+    const int grow = il ? (f / il) * 2 * il + f % il : f;
+    const int urow = il ? grow + il : F + f;
+    const float g = row_dot<T, VEC>(w + (size_t)grow * D, xs, D, lane);
+    const float u = row_dot<T, VEC>(w + (size_t)urow * D, xs, D, lane);
     if (lane == 0) h[((size_t)t * top + k) * F + f] = from_f32<T>(g / (1.0f + expf(-g)) * u);
   }
 }
@@ -110,15 +118,37 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   }
 }
 
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T* __restrict__ xg, int D) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const T* src = x + (size_t)row_token[blockIdx.x] * D;
+  T* dst = xg + (size_t)blockIdx.x * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out,
+                                   int D, int top, int accumulate) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x;
+  const float weight = 1.0f / (float)top;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc += weight * y[(size_t)pair_row[t * top + k] * D + d];
+    out[(size_t)t * D + d] = accumulate ? out[(size_t)t * D + d] + acc : acc;
+  }
+}
+
 namespace {
 
 template <typename T>
-int launch_moe(const void* x, const int* tokens, const int* table, const void* w_gate, const void* w_up,
+int launch_moe(const void* x, const int* tokens, const int* table, const void* w_gu, int il,
                const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
                int accumulate, int* status, cudaStream_t stream) {
   const int per = 16 / (int)sizeof(T);   // elements per 16 bytes
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-  const bool vec_gu = D % 8 == 0 && D % per == 0 && aligned(w_gate) && aligned(w_up);
+  const bool vec_gu = D % 8 == 0 && D % per == 0 && aligned(w_gu);
   const bool vec_dn = F % 8 == 0 && F % per == 0 && aligned(w_down);
   // enough blocks to fill the GPU when the tokens are few, whole experts per block when they are many
   int units = F, outs = D;
@@ -137,7 +167,7 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
     rc = zk_launch_dependent(kern, grid_gu, dim3(MOE_WARPS * 32), smem_gu, stream, (const T*)x, tokens, table,        \
-                             (const T*)w_gate, (const T*)w_up, (T*)h, D, F, top, vocab, n_experts, units, status);    \
+                             (const T*)w_gu, il, (T*)h, D, F, top, vocab, n_experts, units, status);                  \
   } while (0)
 #define ZK_MOE_DN(V)                                                                                                  \
   do {                                                                                                                \
@@ -162,17 +192,37 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
 extern "C" {
 
 // x [n, D], h [n, top, F] (scratch, run dtype), y [n, D] float32 (= or += with `accumulate`);
-// tokens [n] and table [vocab, top] int32; w_gate, w_up [experts, F, D], w_down [experts, D, F].
-int zk_moe_table(const void* x, const int* tokens, const int* table, const void* w_gate, const void* w_up,
+// tokens [n] and table [vocab, top] int32; w_gu [experts, 2F, D] (see `il` above), w_down [experts, D, F].
+int zk_moe_table(const void* x, const int* tokens, const int* table, const void* w_gu, int il,
                  const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
                  int accumulate, int dtype, int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (D <= 0 || F <= 0 || top <= 0 || vocab <= 0 || n_experts <= 0) return ZK_EINVAL;
+  if (D <= 0 || F <= 0 || top <= 0 || vocab <= 0 || n_experts <= 0 || il < 0 || (il > 0 && F % il)) return ZK_EINVAL;
   if (dtype == ZK_F32)
-    return launch_moe<float>(x, tokens, table, w_gate, w_up, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+    return launch_moe<float>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
   if (dtype == ZK_BF16)
-    return launch_moe<bf16>(x, tokens, table, w_gate, w_up, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+    return launch_moe<bf16>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
   return ZK_EINVAL;
+}
+
+// xg[r, :] = x[row_token[r], :] for r < n_rows (rows in the run dtype, D elements).
+int zk_moe_gather(const void* x, const int* row_token, void* xg, int n_rows, int D, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (D <= 0) return ZK_EINVAL;
+  const int threads = 128;
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(moe_gather_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, row_token, (float*)xg, D);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(moe_gather_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)x, row_token, (bf16*)xg, D);
+  return ZK_EINVAL;
+}
+
+// out[t, :] (=|+=) (1/top) * sum_k y[pair_row[t * top + k], :], float32, added in the order of k.
+int zk_moe_combine(const float* y, const int* pair_row, float* out, int n, int D, int top, int accumulate,
+                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (D <= 0 || top <= 0) return ZK_EINVAL;
+  return zk_launch_dependent(moe_combine_kernel, dim3(n), dim3(128), 0, stream, y, pair_row, out, D, top, accumulate);
 }
 
 }  // extern "C"

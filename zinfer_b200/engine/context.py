@@ -66,13 +66,13 @@ class StepContext:
     n_tokens, n_seqs; q_lens (host list: tokens each sequence brings), max_q_len, max_kv_len
     (longest sequence after the step), is_decode (one token for every sequence); the device
     arrays tokens, tok_seq, tok_pos [n_tokens], cu_q [n_seqs + 1], seq_start, seq_slot [n_seqs];
-    `status` (the device's status word) and `sm_count`.  `memo` keeps what parts derive from the
+    `status` (the device's status word), `sm_count`, and `host_tokens` (the ids on the host, or None).  `memo` keeps what parts derive from the
     batch's shape alone (tile tables and the like), so that equal parts derive it once a step; a
     step that is recorded and replayed keeps its memo with the recording."""
 
     def __init__(self, dtype: torch.dtype, device, status: torch.Tensor, buf: torch.Tensor, n_tokens: int,
                  n_seqs: int, q_lens: Sequence[int], max_kv_len: int, memo: Optional[dict] = None,
-                 sm_count: int = 0):
+                 sm_count: int = 0, host_tokens: Optional[np.ndarray] = None):
         self.dtype, self.device, self.status = dtype, device, status
         self.n_tokens, self.n_seqs = n_tokens, n_seqs
         self.q_lens = list(q_lens)
@@ -80,6 +80,9 @@ class StepContext:
         self.max_kv_len = max_kv_len
         self.is_decode = self.max_q_len == 1 and n_tokens == n_seqs
         self.sm_count = sm_count
+        # the step's token ids as the host packed them, or None when only the device knows them (a step that
+        # runs on the tokens the step before sampled); parts may plan with them, never require them
+        self.host_tokens = host_tokens
         self._buf = buf
         lay = batch_layout(n_tokens, n_seqs)
         for name in ("tokens", "tok_seq", "tok_pos", "cu_q", "seq_start", "seq_slot"):

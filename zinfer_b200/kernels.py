@@ -41,7 +41,9 @@ _SIGNATURES = {
         "zk_seqconv_max_taps": "",
     },
     "moe": {
-        "zk_moe_table": "pppppppp" + "iiiiiiiipp",
+        "zk_moe_table": "ppppippp" + "iiiiiiiipp",
+        "zk_moe_gather": "pppiiip",
+        "zk_moe_combine": "pppiiiip",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -71,7 +73,7 @@ _SIGNATURES = {
         "zk_attn_decode_noalloc_bytes": "iiii",
     },
     "attention_prefill": {
-        "zk_attn_prefill": "pppppppppp" + "iiiiiiifp",
+        "zk_attn_prefill": "pppppppppp" + "iiiiiiif" + "pp" + "p",
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
@@ -81,7 +83,7 @@ _SIGNATURES = {
         "zk_attn_prefill_tc5_tile_tokens": "ii",
     },
     "attention_decode_tc": {
-        "zk_attn_decode_tc": "pppppppppiiiiiiifiip",
+        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "p",
         "zk_attn_decode_tc_takes": "iiii",
     },
     "sampling": {
@@ -331,19 +333,19 @@ def seqconv(x: torch.Tensor, state: torch.Tensor, taps: torch.Tensor, tok_seq, c
 
 # ------------------------------------------------------------------------------- experts picked by a table
 
-def moe_table(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+def moe_table(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate_up: torch.Tensor, interleave: int,
               w_down: torch.Tensor, status: torch.Tensor, out: Optional[torch.Tensor] = None,
               accumulate: bool = False) -> torch.Tensor:
     """y[t] = (1/top) sum_k W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = table[tokens[t]][k].
-    x [n, D] run dtype; table int32 [vocab, top]; w_gate, w_up [E, F, D], w_down [E, D, F]; y float32 [n, D]."""
+    x [n, D] run dtype; table int32 [vocab, top]; w_gate_up [E, 2F, D], an expert's rows [gate | up] or, with
+    `interleave` = g, groups of g gate rows followed by their g up rows; w_down [E, D, F]; y float32 [n, D]."""
     _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
     n, D = x.shape
     _need(tokens, "tokens", torch.int32, (n,))
     _need(table, "table", torch.int32, (None, None))
     vocab, top = table.shape
-    _need(w_gate, "w_gate", x.dtype, (None, None, D))
-    E, F, _ = w_gate.shape
-    _need(w_up, "w_up", x.dtype, (E, F, D))
+    _need(w_gate_up, "w_gate_up", x.dtype, (None, None, D))
+    E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
     _need(w_down, "w_down", x.dtype, (E, D, F))
     if out is None:
         if accumulate:
@@ -351,7 +353,7 @@ def moe_table(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate
         out = torch.empty((n, D), dtype=torch.float32, device=x.device)
     _need(out, "out", torch.float32, (n, D))
     h = torch.empty((n, top, F), dtype=x.dtype, device=x.device)
-    _check(_fn("moe", "zk_moe_table")(_ptr(x), _ptr(tokens), _ptr(table), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(h),
+    _check(_fn("moe", "zk_moe_table")(_ptr(x), _ptr(tokens), _ptr(table), _ptr(w_gate_up), int(interleave), _ptr(w_down), _ptr(h),
                                       _ptr(out), n, D, F, top, vocab, E, 1 if accumulate else 0, dtype_code(x.dtype),
                                       _ptr(status), _stream()), "moe_table")
     return out
@@ -737,6 +739,26 @@ def conv_decode(bcx, state, w, bias, seq_slot, interleave: int = 0) -> torch.Ten
     return y
 
 
+def moe_gather(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
+    """xg[r] = x[row_token[r]]: rows in the order a grouped contraction wants them."""
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
+    _need(row_token, "row_token", torch.int32)
+    xg = torch.empty((row_token.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(_fn("moe", "zk_moe_gather")(_ptr(x), _ptr(row_token), _ptr(xg), row_token.numel(), x.shape[1],
+                                       dtype_code(x.dtype), _stream()), "moe_gather")
+    return xg
+
+
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[t] (+)= (1/top) sum_k y[pair_row[t * top + k]], float32, added in the order of k."""
+    _need(y, "y", torch.float32, (None, None))
+    _need(out, "out", torch.float32, (None, y.shape[1]))
+    _need(pair_row, "pair_row", torch.int32, (out.shape[0] * top,))
+    _check(_fn("moe", "zk_moe_combine")(_ptr(y), _ptr(pair_row), _ptr(out), out.shape[0], y.shape[1], top,
+                                        1 if accumulate else 0, _stream()), "moe_combine")
+    return out
+
+
 # ------------------------------------------------------------------------------- attention
 
 def attn_rows_per_block() -> int:
@@ -846,15 +868,16 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
                    biased: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
-    Values of another width than the keys, or a distance bias on the scores, go to the general kernel."""
-    plain = (value_dim is None or value_dim == head_dim) and not biased
-    if plain and dtype == torch.bfloat16 and n_heads % n_kv == 0:
-        if (not single_token and window <= 0 and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+    Values of another width than the keys go to the general kernel; a distance bias on the scores is
+    taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc")."""
+    same_width = value_dim is None or value_dim == head_dim
+    if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
+        if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
-        if single_token and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
+        if single_token and not biased and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token", 1
         if not single_token and _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim, page_size):
             return "prompt_tc", _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_kv)
@@ -881,8 +904,11 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if bias is not None:
         for b, nm in zip(bias, ("bias r1", "bias r2")):
             _need(b, nm, torch.float32, (n_heads,))
-    if (vd != head_dim or bias is not None) and kind not in (None, "general"):
-        raise KernelError(f"attention: the '{kind}' kernel takes neither a value width of its own nor a distance bias")
+    if vd != head_dim and kind not in (None, "general"):
+        raise KernelError(f"attention: the '{kind}' kernel takes no value width of its own")
+    if bias is not None and kind not in (None, "general", "prompt_tc", "single_token_tc"):
+        raise KernelError(f"attention: the '{kind}' kernel takes no distance bias")
+    r1, r2 = (_ptr(bias[0]), _ptr(bias[1])) if bias is not None else (None, None)
     page_size = k_cache.shape[2]
     if n_heads % n_kv:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv} KV heads")
@@ -893,8 +919,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     bq, gc = attn_tile_shape(n_heads, n_kv)
     n_tiles = tile_seq.numel()
     out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
-    general_only = vd != head_dim or bias is not None
-    if general_only:
+    if vd != head_dim or (bias is not None and kind != "single_token_tc"):
         single_token = False        # the general kernel runs single tokens as tiles of one query
     part_o = part_ml = None
     if num_splits > 1:
@@ -918,14 +943,14 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention_prefill", "zk_attn_prefill")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
-            page_size, window, scale, _stream()), "attention (prompt, tensor cores)")
+            page_size, window, scale, r1, r2, _stream()), "attention (prompt, tensor cores)")
         return out
     if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
             and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
-            scale, num_splits, split_keys, _stream()), "attention (single token, tensor cores)")
+            scale, num_splits, split_keys, r1, r2, _stream()), "attention (single token, tensor cores)")
         if num_splits > 1:
             _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
                                                      num_splits, dtype_code(q.dtype), _stream()), "attention merge")
@@ -945,8 +970,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     _check(_fn("attention", "zk_attn_fwd")(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
-        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd,
-        _ptr(bias[0]) if bias else None, _ptr(bias[1]) if bias else None, _stream()),
+        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd, r1, r2, _stream()),
         "attention")
     if num_splits > 1:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,

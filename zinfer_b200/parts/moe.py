@@ -6,17 +6,31 @@ weight 1/top (no router, nothing learned at run time decides):
 plus, optionally, a shared expert of the same form that every token takes, weighed by one number
 per token: y_t += sigmoid(g . x_t) * Shared(x_t), the gate in float32 on the float32 rows.
 
-The experts' matrices are stacked at load ([experts, rows, cols]); the kernels find a token's experts
-through the table on the device, so the step needs nothing from the host and can be recorded.  The
-part reads the token ids of the step from the step context (`ctx.tokens`)."""
+The experts' matrices are stacked at load (gate and up as one [experts, 2F, D] tensor in the layout of
+`SwiGLU`, down as [experts, D, F]).  Two ways to run, which agree to rounding:
+
+* few tokens (single-token steps): two weight-streaming kernels find a token's experts through the table
+  on the device (`ctx.tokens`), so the step needs nothing from the host and can be recorded;
+* many tokens (prompt steps): which expert a token takes is a function of its id alone, and the ids of a
+  prompt step are known on the host when the step is packed (`ctx.host_tokens`).  The rows are gathered in
+  the order of their experts, each expert runs as an ordinary `SwiGLU` over its contiguous rows (the
+  tensor-core contractions with the activation in their epilogue), and a last kernel sums each token's
+  `top` rows in the order of k.  No device-to-host copy is involved."""
 from __future__ import annotations
 
 from typing import Optional
 
+import numpy as np
 import torch
 
 from .. import kernels
 from .base import FEED_FORWARDS, FeedForward, WeightSpec
+from .feedforward import SwiGLU
+from .linear import FUSION_GROUP, interleave_rows
+
+# From this many tokens on a step whose ids the host knows runs expert by expert.  Below it the streaming
+# kernels, which read an expert's weights once per (token, k), are faster than 2 launches per expert.
+GROUPED_MIN_TOKENS = 96
 
 
 class TableMoE(FeedForward):
@@ -34,7 +48,9 @@ class TableMoE(FeedForward):
         self.shared, self.shared_gate_name = shared, shared_gate_name
         if shared is None and shared_gate_name is not None:
             raise ValueError("a shared-expert gate without a shared expert")
-        self.table = self.w_gate = self.w_up = self.w_down = self.shared_gate = None
+        self.table = self.table_host = self.w_gate_up = self.w_down = self.shared_gate = None
+        self.interleave = FUSION_GROUP if ffn_dim % FUSION_GROUP == 0 else 0
+        self.experts: list[SwiGLU] = []         # views of the stacked tensors, one ordinary feed-forward per expert
 
     def parts(self):
         return [self.shared] if self.shared is not None else []
@@ -50,16 +66,26 @@ class TableMoE(FeedForward):
 
     def load(self, weights, dtype, device):
         self.table = weights[self.table_name].contiguous()
-        self.w_gate = torch.stack([weights[g] for g, _, _ in self.names]).contiguous()
-        self.w_up = torch.stack([weights[u] for _, u, _ in self.names]).contiguous()
+        self.table_host = self.table.cpu().numpy()
+        stack = (lambda g, u: interleave_rows([g, u])) if self.interleave else (lambda g, u: torch.cat([g, u], dim=0))
+        self.w_gate_up = torch.stack([stack(weights[g], weights[u]) for g, u, _ in self.names]).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in self.names]).contiguous()
+        self.experts = []
+        for e in range(self.n_experts):
+            ff = SwiGLU(self.hidden, self.ffn_dim, "", "", "")
+            ff.w_gate_up, ff.w_down = self.w_gate_up[e], self.w_down[e]
+            self.experts.append(ff)
         if self.shared_gate_name is not None:
             self.shared_gate = weights[self.shared_gate_name].reshape(self.hidden).contiguous()
 
     def forward(self, ctx, xn, out, accumulate):
         rows = xn if xn.dtype == ctx.dtype else kernels.cast_rows(xn, ctx.dtype)
-        kernels.moe_table(rows, ctx.tokens, self.table, self.w_gate, self.w_up, self.w_down, ctx.status, out=out,
-                          accumulate=accumulate)
+        host_tokens = getattr(ctx, "host_tokens", None)
+        if host_tokens is not None and rows.shape[0] >= GROUPED_MIN_TOKENS:
+            self._expert_by_expert(ctx, rows, host_tokens, out, accumulate)
+        else:
+            kernels.moe_table(rows, ctx.tokens, self.table, self.w_gate_up, self.interleave, self.w_down, ctx.status,
+                              out=out, accumulate=accumulate)
         if self.shared is None:
             return
         if self.shared_gate is None:
@@ -70,6 +96,33 @@ class TableMoE(FeedForward):
         branch = torch.empty_like(out)
         self.shared.forward(ctx, rows, branch, False)
         kernels.gate_add(xn, self.shared_gate, branch, out)
+
+    def routing(self, host_tokens: np.ndarray):
+        """For token ids known on the host: (row_token [n * top]: the token of each row when the (token, k)
+        pairs are sorted by expert, keeping their order within an expert; pair_row [n * top]: where pair
+        t * top + k went; bounds [experts + 1]: expert e owns rows bounds[e] .. bounds[e + 1])."""
+        ids = np.clip(np.asarray(host_tokens, dtype=np.int64), 0, self.vocab - 1)   # a bad id is flagged by the embedding
+        experts = np.clip(self.table_host[ids].reshape(-1), 0, self.n_experts - 1)
+        order = np.argsort(experts, kind="stable")
+        pair_row = np.empty_like(order)
+        pair_row[order] = np.arange(order.size)
+        bounds = np.concatenate([[0], np.cumsum(np.bincount(experts, minlength=self.n_experts))])
+        return (order // self.top).astype(np.int32), pair_row.astype(np.int32), bounds
+
+    def _expert_by_expert(self, ctx, rows, host_tokens, out, accumulate):
+        def make():
+            row_token, pair_row, bounds = self.routing(host_tokens)
+            both = torch.from_numpy(np.concatenate([row_token, pair_row])).pin_memory().to(ctx.device, non_blocking=True)
+            return both[:row_token.size], both[row_token.size:], bounds
+
+        row_token, pair_row, bounds = ctx.memo(("expert rows", id(self)), make)
+        xg = kernels.moe_gather(rows, row_token)
+        y = torch.empty((xg.shape[0], self.hidden), dtype=torch.float32, device=xg.device)
+        for e, ff in enumerate(self.experts):
+            r0, r1 = int(bounds[e]), int(bounds[e + 1])
+            if r1 > r0:
+                ff.forward(ctx, xg[r0:r1], y[r0:r1], False)
+        kernels.moe_combine(y, pair_row, self.top, out, accumulate)
 
 
 FEED_FORWARDS.register("table_moe", TableMoE)
