@@ -231,6 +231,97 @@ def secondary_arm(args) -> dict:
             "graph_captures_in_timed_steps": captures, "wall_s_with_prompts": round(wall, 1)}
 
 
+# Ponusun beside the closest existing architecture at equal size: width, layers, heads, window and vocabulary
+# are the same, and LFM2's SwiGLU is as wide as the experts one Ponusun token runs (top * ff + shared).
+PONUSUN_SIZES = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv=4, dim=64, window=512, experts=16, top=2, ff=1024, shared=1024,
+                  dense_ff=4096, vocab=32768, taps=4),
+    "w2048": dict(width=2048, layers=8, heads=32, kv=8, dim=64, window=1024, experts=16, top=2, ff=2048, shared=2048,
+                  dense_ff=8192, vocab=65536, taps=4),
+}
+
+
+def ponusun_config(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                 "mask": {"size": sz["window"]}}
+        if i >= 2 and i % 2 == 0:
+            mixer["kv_from"] = i - 1                   # every second layer reads the keys and values of the one before
+        mlp = ({"kind": "dense", "ff": sz["dense_ff"]} if i == 0 else
+               {"kind": "moe", "expert": {"ff": sz["ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]},
+                "shared": {"ff": sz["shared"]}})
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Ponusun", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "canon": {"taps": sz["taps"]}, "logit_softcap": 30.0, "layers": layers}
+
+
+def lfm2_like(sz: dict) -> dict:
+    return dict(LFM2_1_2B, vocab_size=sz["vocab"], hidden_size=sz["width"], num_hidden_layers=sz["layers"],
+                num_attention_heads=sz["heads"], num_key_value_heads=sz["kv"], head_dim=sz["dim"],
+                max_position_embeddings=CONTEXT, layer_types=["sliding_attention"] * sz["layers"],
+                sliding_window=sz["window"], block_ff_dim=sz["top"] * sz["ff"] + sz["shared"], block_auto_adjust_ff_dim=False)
+
+
+def ponusun_arm(args) -> dict:
+    """Prompt and single-token throughput of Ponusun and of LFM2 at equal size, random weights, bfloat16:
+    one prompt of --prefill-tokens tokens in one step (median of 5), then --steps single-token steps of
+    --batch sequences replayed from CUDA graphs (prompts of 512..2,048 tokens)."""
+    import numpy as np
+    import torch
+    import zinfer_b200 as z
+    from zinfer_b200 import kernels
+
+    kernels.require_cuda()
+    out = {"metric": "prompt and single-token tokens/s, Ponusun beside LFM2 at equal size (random weights)", "unit": "tokens/s",
+           "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup, "batch": args.batch,
+           "prefill_tokens": args.prefill_tokens, "sizes": {}}
+    wanted = [args.size] if args.size else list(PONUSUN_SIZES)
+    with ClockSampler() as clocks:
+        for name in wanted:
+            sz = PONUSUN_SIZES[name]
+            row = {}
+            for arch, cfg_dict in (("ponusun", ponusun_config(sz)), ("lfm2", lfm2_like(sz))):
+                if args.arch and arch != args.arch:
+                    continue
+                cfg = z.config_from_dict(cfg_dict)
+                model = z.random(cfg, seed=0, dtype="bf16", fill_on_device=True, std=sz["width"] ** -0.5)
+                engine = z.Engine(model, max_batch=args.batch, max_seq_len=CONTEXT, use_graphs=not args.no_graphs)
+                rng = np.random.default_rng(0)
+                res = {}
+                if args.only in ("all", "prefill"):
+                    toks = rng.integers(0, cfg.vocab_size, size=args.prefill_tokens).tolist()
+                    times = []
+                    for i in range(args.warmup + 5):
+                        slot = engine.start(1)
+                        torch.cuda.synchronize()
+                        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        start.record()
+                        engine.step(slot, [toks], check=False)
+                        stop.record()
+                        torch.cuda.synchronize()
+                        engine.finish(slot)
+                        if i >= args.warmup:
+                            times.append(start.elapsed_time(stop))
+                    engine.check_status()
+                    ms = statistics.median(times)
+                    res["prefill"] = {"tokens_per_s": round(args.prefill_tokens / (ms * 1e-3), 1), "ms": round(ms, 3)}
+                if args.only in ("all", "decode"):
+                    ms, cached, launches, captures = time_decode(engine, torch, rng, args.batch, args.steps, args.warmup,
+                                                                 cfg.vocab_size)
+                    res["decode"] = {"tokens_per_s": round(args.batch / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
+                                     "launches_per_step": launches, "graph_captures_in_timed_steps": captures}
+                row[arch] = res
+                del engine, model
+                torch.cuda.empty_cache()
+            if "ponusun" in row and "lfm2" in row:
+                row["ponusun_over_lfm2"] = {k: round(row["ponusun"][k]["tokens_per_s"] / row["lfm2"][k]["tokens_per_s"], 3)
+                                            for k in row["ponusun"]}
+            out["sizes"][name] = dict(row, config={k: sz[k] for k in sz})
+    out["clocks"] = clocks.summary()
+    return out
+
+
 def own_arm(args) -> dict:
     import numpy as np
     import torch
@@ -332,8 +423,11 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: the prompt's length (the headline line always uses 2,048)")
-    ap.add_argument("--model", default="1.2b", choices=["1.2b"] + sorted(SECONDARY),
-                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only)")
+    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun"] + sorted(SECONDARY),
+                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun: the "
+                         "Ponusun architecture beside LFM2 at equal size, prompt and single-token steps")
+    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun: one size only")
+    ap.add_argument("--arch", default="", choices=["", "ponusun", "lfm2"], help="with --model ponusun: one architecture only")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
@@ -344,6 +438,9 @@ def main() -> int:
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: zinfer_b200 runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.model == "ponusun":
+        print(json.dumps(ponusun_arm(args)))
+        return 0
     print(json.dumps(own_arm(args) if args.model == "1.2b" else secondary_arm(args)))
     return 0
 

@@ -59,6 +59,9 @@ struct Params {
   const float* emit_w;
   bf16* emit_x;
   float* emit_ssq;
+  // Grouped products (normal mode, one tile per block): W is [groups, N, K] and the 128 rows of token tile t
+  // are multiplied with the matrix of group tile_group[t]; null = one matrix for all rows.
+  const int* tile_group;
 };
 
 // q[j] of every lane, j < T (T = 4, 8 or 16): the sums over the warp's 32 lanes, T - 1 + log2(32 / T)
@@ -162,7 +165,12 @@ __global__ void __launch_bounds__(THREADS)
     // for the kernel before and request the rows.
     const CUtensorMap* map_w = SWAP ? &map_a : &map_b;
     const CUtensorMap* map_x = SWAP ? &map_b : &map_a;
-    const int w_row = SWAP ? a_tile * BM : b_tile * BN, x_row = SWAP ? b_tile * BN : a_tile * BM;
+    int w_row = SWAP ? a_tile * BM : b_tile * BN;
+    const int x_row = SWAP ? b_tile * BN : a_tile * BM;
+    if (!SWAP && p.tile_group) {       // which matrix the tile takes was written by the step itself: wait first
+      zk_wait_prior();
+      w_row += p.tile_group[a_tile] * p.N;
+    }
     constexpr int W_OFF = SWAP ? 0 : S::A_BYTES, X_OFF = SWAP ? S::A_BYTES : 0;
     const int pre = min(STAGES, kb1 - kb0);
     for (int it = 0; it < pre; ++it) {
@@ -183,8 +191,8 @@ __global__ void __launch_bounds__(THREADS)
       if (*aborted) break;
       unsigned char* a_dst = tiles + (size_t)s * S::STAGE_BYTES;
       mbar_expect_tx(&full[s], S::STAGE_BYTES);
-      tma_load_2d(a_dst, &map_a, kb * BK, a_tile * BM, &full[s]);
-      tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN, &full[s]);
+      tma_load_2d(a_dst, &map_a, kb * BK, SWAP ? a_tile * BM : x_row, &full[s]);
+      tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, SWAP ? b_tile * BN : w_row, &full[s]);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
@@ -924,6 +932,29 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   if (bn == 32) { ZK_TC_SWAP(32) }
   ZK_TC_SWAP(64)
 #undef ZK_TC_SWAP
+}
+
+// Grouped product: X [M, K] holds token tiles of 128 rows (M a multiple of 128), W [groups, N, K] contiguous
+// matrices, tile_group [M / 128] (device, int32) names each tile's matrix; C [M, N] (or [M, N/2] with
+// `swiglu`, W's rows then being groups of 16 gate rows and their 16 up rows), bfloat16 or float32.
+int zk_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int K, int groups, int ldx, int ldc,
+                       int out_dtype, int swiglu, const int* tile_group, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M % BM || groups <= 0 || !tile_group || !status) return ZK_EINVAL;
+  if (K <= 0 || K % 8 || ldx % 8 || ldx < K || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 32)) return ZK_EINVAL;
+  if ((long long)groups * N > 0x7fffffffLL) return ZK_EINVAL;
+  if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)C) % 16) return ZK_EINVAL;
+  if (out_dtype != ZK_F32 && out_dtype != ZK_BF16) return ZK_EINVAL;
+  Params p{};
+  p.C = C; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = 1; p.swiglu = swiglu;
+  p.tile_group = tile_group;
+  constexpr int BN = 128;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, groups * N, K, K, BN)) return ZK_EINVAL;
+  dim3 grid(M / BM, ceil_div_i(N, BN), 1);
+  return out_dtype == ZK_F32 ? launch<BN, 3, false, float>(ma, mb, p, grid, stream)
+                             : launch<BN, 3, false, bf16>(ma, mb, p, grid, stream);
 }
 
 // Forces the form of products with more than 64 rows and N a multiple of 256: 0 one 128 x 128 tile

@@ -37,23 +37,41 @@ template <> struct Vec8<float> {
   }
 };
 
-// dot of a weight row with the row staged in shared memory (float32), lanes striding; VEC: rows are
-// 16-byte aligned and K a multiple of 8.
-template <typename T, bool VEC>
-__device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int K, int lane) {
-  float acc = 0.f;
+// R dot products at once: weight rows w[0..R) with the row staged in shared memory (float32), lanes
+// striding.  All R loads of a step are requested before the first is used, so a warp keeps R x 512 bytes
+// in flight; one row at a time the kernel waited for memory once per row.  VEC: rows are 16-byte aligned
+// and K a multiple of 8.  Each sum is added in the same order whatever R is and whichever rows share the call.
+template <typename T, bool VEC, int R>
+__device__ __forceinline__ void rows_dot(const T* const (&w)[R], const float* __restrict__ xs, int K, int lane,
+                                         float (&out)[R]) {
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
   if (VEC) {
     for (int k = lane * 8; k < K; k += 256) {
-      float v[8];
-      Vec8<T>::load(w + k, v);
+      float v[R][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc = fmaf(v[i], xs[k + i], acc);
+      for (int r = 0; r < R; ++r) Vec8<T>::load(w[r] + k, v[r]);
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = xs[k + i];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[r] = fmaf(v[r][i], x[i], acc[r]);
     }
   } else {
-    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), xs[k], acc);
+    for (int k = lane; k < K; k += 32) {
+      const float x = xs[k];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = fmaf(to_f32(w[r][k]), x, acc[r]);
+    }
   }
-  return warp_sum(acc);
+#pragma unroll
+  for (int r = 0; r < R; ++r) out[r] = warp_sum(acc[r]);
 }
+
+#define MOE_UNITS 4      // hidden units (gate and up row each) or outputs a warp works on at once
 
 __device__ __forceinline__ int moe_expert(const int* __restrict__ tokens, const int* __restrict__ table, int t, int k,
                                           int top, int vocab, int n_experts, int* status) {
@@ -82,12 +100,28 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   __syncthreads();
   const T* w = w_gu + (size_t)e * 2 * F * D;
   const int f0 = blockIdx.y * units_per_block, f1 = min(F, f0 + units_per_block);
-  for (int f = f0 + warp; f < f1; f += MOE_WARPS) {
-    const int grow = il ? (f / il) * 2 * il + f % il : f;
-    const int urow = il ? grow + il : F + f;
-    const float g = row_dot<T, VEC>(w + (size_t)grow * D, xs, D, lane);
-    const float u = row_dot<T, VEC>(w + (size_t)urow * D, xs, D, lane);
-    if (lane == 0) h[((size_t)t * top + k) * F + f] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  for (int fb = f0 + warp * MOE_UNITS; fb < f1; fb += MOE_WARPS * MOE_UNITS) {
+    const T* rows[2 * MOE_UNITS];
+#pragma unroll
+    for (int u = 0; u < MOE_UNITS; ++u) {
+      const int f = min(fb + u, f1 - 1);        // a unit beyond the slice repeats the last one and is not written
+      const int grow = il ? (f / il) * 2 * il + f % il : f;
+      const int urow = il ? grow + il : F + f;
+      rows[2 * u] = w + (size_t)grow * D;
+      rows[2 * u + 1] = w + (size_t)urow * D;
+    }
+    float dot[2 * MOE_UNITS];
+    rows_dot<T, VEC, 2 * MOE_UNITS>(rows, xs, D, lane, dot);
+    if (lane < MOE_UNITS && fb + lane < f1) {
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int i = 0; i < MOE_UNITS; ++i)
+        if (lane == i) {
+          g = dot[2 * i];
+          u = dot[2 * i + 1];
+        }
+      h[((size_t)t * top + k) * F + fb + lane] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
   }
 }
 
@@ -105,15 +139,27 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   __syncthreads();
   const float weight = 1.0f / (float)top;
   const int d0 = blockIdx.y * outs_per_block, d1 = min(D, d0 + outs_per_block);
-  for (int d = d0 + warp; d < d1; d += MOE_WARPS) {
-    float acc = 0.f;
+  for (int db = d0 + warp * MOE_UNITS; db < d1; db += MOE_WARPS * MOE_UNITS) {
+    float acc[MOE_UNITS];
+#pragma unroll
+    for (int u = 0; u < MOE_UNITS; ++u) acc[u] = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
-      acc += weight * row_dot<T, VEC>(w_down + ((size_t)e * D + d) * F, hs + (size_t)k * F, F, lane);
+      const T* rows[MOE_UNITS];
+#pragma unroll
+      for (int u = 0; u < MOE_UNITS; ++u) rows[u] = w_down + ((size_t)e * D + min(db + u, d1 - 1)) * F;
+      float dot[MOE_UNITS];
+      rows_dot<T, VEC, MOE_UNITS>(rows, hs + (size_t)k * F, F, lane, dot);
+#pragma unroll
+      for (int u = 0; u < MOE_UNITS; ++u) acc[u] += weight * dot[u];
     }
-    if (lane == 0) {
-      float* dst = y + (size_t)t * D + d;
-      *dst = accumulate ? *dst + acc : acc;
+    if (lane < MOE_UNITS && db + lane < d1) {
+      float v = 0.f;
+#pragma unroll
+      for (int u = 0; u < MOE_UNITS; ++u)
+        if (lane == u) v = acc[u];
+      float* dst = y + (size_t)t * D + db + lane;
+      *dst = accumulate ? *dst + v : v;
     }
   }
 }
@@ -122,9 +168,10 @@ template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T* __restrict__ xg, int D) {
   zk_let_next_start();
   zk_wait_prior();
-  const T* src = x + (size_t)row_token[blockIdx.x] * D;
+  const int t = row_token[blockIdx.x];       // < 0: a padding row
+  const T* src = x + (size_t)(t < 0 ? 0 : t) * D;
   T* dst = xg + (size_t)blockIdx.x * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = t < 0 ? from_f32<T>(0.f) : src[d];
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out,
@@ -153,8 +200,11 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
   // enough blocks to fill the GPU when the tokens are few, whole experts per block when they are many
   int units = F, outs = D;
   const long long pairs = (long long)n * top;
-  while (units > MOE_WARPS && pairs * ((F + units - 1) / units) < 2 * 148) units = (units + 1) / 2;
-  while (outs > MOE_WARPS && (long long)n * ((D + outs - 1) / outs) < 2 * 148) outs = (outs + 1) / 2;
+  constexpr int GRAIN = MOE_WARPS * MOE_UNITS;     // what a block's warps take in one round
+  while (units > GRAIN && pairs * ((F + units - 1) / units) < 2 * 148) units = (units + 1) / 2;
+  while (outs > GRAIN && (long long)n * ((D + outs - 1) / outs) < 2 * 148) outs = (outs + 1) / 2;
+  units = (units + GRAIN - 1) / GRAIN * GRAIN;
+  outs = (outs + GRAIN - 1) / GRAIN * GRAIN;
   const size_t smem_gu = sizeof(float) * D, smem_dn = sizeof(float) * (size_t)top * F;
   if (smem_gu > 200 * 1024 || smem_dn > 200 * 1024) return ZK_EINVAL;
   const dim3 grid_gu((unsigned)pairs, (F + units - 1) / units), grid_dn(n, (D + outs - 1) / outs);
@@ -205,7 +255,7 @@ int zk_moe_table(const void* x, const int* tokens, const int* table, const void*
   return ZK_EINVAL;
 }
 
-// xg[r, :] = x[row_token[r], :] for r < n_rows (rows in the run dtype, D elements).
+// xg[r, :] = x[row_token[r], :] for r < n_rows, zeros where row_token[r] < 0 (rows in the run dtype, D elements).
 int zk_moe_gather(const void* x, const int* row_token, void* xg, int n_rows, int D, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (D <= 0) return ZK_EINVAL;

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "gemm_tc": {
         "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "pp",
         "zk_gemm_tc_force_form": "i",
+        "zk_gemm_tc_grouped": "pppiiiiiiiippp",
     },
     "shortconv": {
         "zk_conv_forward": "ppppppppiiiliip",
@@ -504,6 +505,36 @@ def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=No
     return out
 
 
+GEMM_TC_GROUP_ROWS = 128       # rows per token tile of a grouped product
+
+
+def gemm_tc_grouped_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 3 and w.is_contiguous()
+            and a.is_contiguous() and a.shape[1] == w.shape[2] and a.shape[1] % 8 == 0 and a.shape[0] % GEMM_TC_GROUP_ROWS == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, swiglu: bool = False,
+                    out_dtype=torch.bfloat16) -> torch.Tensor:
+    """out[rows of tile t] = a[rows of tile t] @ w[tile_group[t]].T on the tcgen05 kernel: a [M, K] bfloat16 in
+    tiles of 128 rows, w [groups, N, K] bfloat16, tile_group int32 [M / 128] on the device.  With `swiglu`
+    every w[g] holds groups of 16 gate rows and their 16 up rows and the result is silu(gate) * up, [M, N/2]."""
+    if not gemm_tc_grouped_takes(a, w):
+        raise KernelError(f"gemm_tc_grouped: a {tuple(a.shape)} / w {tuple(w.shape)} need bfloat16, whole tiles of "
+                          f"{GEMM_TC_GROUP_ROWS} rows, K a multiple of 8")
+    M, K = a.shape
+    G, N, _ = w.shape
+    _need(tile_group, "tile_group", torch.int32, (M // GEMM_TC_GROUP_ROWS,))
+    if swiglu and N % 32:
+        raise KernelError("gemm_tc_grouped: the SwiGLU epilogue needs N a multiple of 32")
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=a.device)
+    _need(out, "out", (torch.float32, torch.bfloat16))
+    _check(_fn("gemm_tc", "zk_gemm_tc_grouped")(_ptr(a), _ptr(w), _ptr(out), M, N, K, G, a.stride(0), out.stride(0),
+                                                dtype_code(out.dtype), 1 if swiglu else 0, _ptr(tile_group),
+                                                _ptr(status_word(a.device)), _stream()), "gemm_tc_grouped")
+    return out
+
+
 def gemm_tc_force_form(form: int) -> None:
     """For measurements and tests: the form that products of more than 64 rows with N a multiple of
     256 take.  0 = one 128 x 128 tile per block, 256 = persistent blocks with 128 x 256 tiles, 512 =
@@ -740,7 +771,7 @@ def conv_decode(bcx, state, w, bias, seq_slot, interleave: int = 0) -> torch.Ten
 
 
 def moe_gather(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
-    """xg[r] = x[row_token[r]]: rows in the order a grouped contraction wants them."""
+    """xg[r] = x[row_token[r]] (zeros where row_token[r] < 0): rows in the order a grouped contraction wants them."""
     _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
     _need(row_token, "row_token", torch.int32)
     xg = torch.empty((row_token.numel(), x.shape[1]), dtype=x.dtype, device=x.device)

@@ -13,9 +13,11 @@ The experts' matrices are stacked at load (gate and up as one [experts, 2F, D] t
   on the device (`ctx.tokens`), so the step needs nothing from the host and can be recorded;
 * many tokens (prompt steps): which expert a token takes is a function of its id alone, and the ids of a
   prompt step are known on the host when the step is packed (`ctx.host_tokens`).  The rows are gathered in
-  the order of their experts, each expert runs as an ordinary `SwiGLU` over its contiguous rows (the
-  tensor-core contractions with the activation in their epilogue), and a last kernel sums each token's
-  `top` rows in the order of k.  No device-to-host copy is involved."""
+  the order of their experts, every expert's rows padded to whole tiles of 128, and ONE grouped tcgen05
+  contraction per matrix runs all experts (each token tile against its expert's matrix; the activation is
+  the first one's epilogue); a last kernel sums each token's `top` rows in the order of k.  Where the grouped
+  kernel does not take the sizes or the dtype (32-bit), each expert runs as an ordinary `SwiGLU` over its
+  contiguous rows instead.  No device-to-host copy is involved either way."""
 from __future__ import annotations
 
 from typing import Optional
@@ -97,31 +99,50 @@ class TableMoE(FeedForward):
         self.shared.forward(ctx, rows, branch, False)
         kernels.gate_add(xn, self.shared_gate, branch, out)
 
-    def routing(self, host_tokens: np.ndarray):
-        """For token ids known on the host: (row_token [n * top]: the token of each row when the (token, k)
-        pairs are sorted by expert, keeping their order within an expert; pair_row [n * top]: where pair
-        t * top + k went; bounds [experts + 1]: expert e owns rows bounds[e] .. bounds[e + 1])."""
+    def routing(self, host_tokens: np.ndarray, tile: int = 1):
+        """For token ids known on the host: (row_token [rows]: the token of each row when the (token, k)
+        pairs are sorted by expert, keeping their order within an expert, -1 for a padding row; pair_row
+        [n * top]: the row pair t * top + k went to; bounds [experts + 1]: expert e owns rows bounds[e] ..
+        bounds[e + 1]).  Every expert's rows are padded to a multiple of `tile`."""
         ids = np.clip(np.asarray(host_tokens, dtype=np.int64), 0, self.vocab - 1)   # a bad id is flagged by the embedding
         experts = np.clip(self.table_host[ids].reshape(-1), 0, self.n_experts - 1)
         order = np.argsort(experts, kind="stable")
-        pair_row = np.empty_like(order)
-        pair_row[order] = np.arange(order.size)
-        bounds = np.concatenate([[0], np.cumsum(np.bincount(experts, minlength=self.n_experts))])
-        return (order // self.top).astype(np.int32), pair_row.astype(np.int32), bounds
+        counts = np.bincount(experts, minlength=self.n_experts)
+        padded = -(-counts // tile) * tile
+        bounds = np.concatenate([[0], np.cumsum(padded)])
+        starts = np.concatenate([[0], np.cumsum(counts)])[:-1]
+        sorted_experts = experts[order]
+        rows = bounds[sorted_experts] + (np.arange(order.size) - starts[sorted_experts])     # row of each sorted pair
+        row_token = np.full(int(bounds[-1]), -1, dtype=np.int32)
+        row_token[rows] = order // self.top
+        pair_row = np.empty(order.size, dtype=np.int32)
+        pair_row[order] = rows
+        return row_token, pair_row, bounds
 
     def _expert_by_expert(self, ctx, rows, host_tokens, out, accumulate):
-        def make():
-            row_token, pair_row, bounds = self.routing(host_tokens)
-            both = torch.from_numpy(np.concatenate([row_token, pair_row])).pin_memory().to(ctx.device, non_blocking=True)
-            return both[:row_token.size], both[row_token.size:], bounds
+        tile = kernels.GEMM_TC_GROUP_ROWS
+        grouped = (self.interleave and rows.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.ffn_dim % 8 == 0
+                   and rows.is_contiguous())
 
-        row_token, pair_row, bounds = ctx.memo(("expert rows", id(self)), make)
+        def make():
+            row_token, pair_row, bounds = self.routing(host_tokens, tile if grouped else 1)
+            tile_group = np.repeat(np.arange(self.n_experts), np.diff(bounds) // tile).astype(np.int32) if grouped \
+                else np.zeros(0, dtype=np.int32)
+            sizes = np.cumsum([row_token.size, pair_row.size, tile_group.size])
+            dev = torch.from_numpy(np.concatenate([row_token, pair_row, tile_group])).pin_memory().to(ctx.device, non_blocking=True)
+            return dev[:sizes[0]], dev[sizes[0]:sizes[1]], dev[sizes[1]:sizes[2]], bounds
+
+        row_token, pair_row, tile_group, bounds = ctx.memo(("expert rows", id(self)), make)
         xg = kernels.moe_gather(rows, row_token)
-        y = torch.empty((xg.shape[0], self.hidden), dtype=torch.float32, device=xg.device)
-        for e, ff in enumerate(self.experts):
-            r0, r1 = int(bounds[e]), int(bounds[e + 1])
-            if r1 > r0:
-                ff.forward(ctx, xg[r0:r1], y[r0:r1], False)
+        if grouped:
+            h = kernels.gemm_tc_grouped(xg, self.w_gate_up, tile_group, swiglu=True)
+            y = kernels.gemm_tc_grouped(h, self.w_down, tile_group, out_dtype=torch.float32)
+        else:
+            y = torch.empty((xg.shape[0], self.hidden), dtype=torch.float32, device=xg.device)
+            for e, ff in enumerate(self.experts):
+                r0, r1 = int(bounds[e]), int(bounds[e + 1])
+                if r1 > r0:
+                    ff.forward(ctx, xg[r0:r1], y[r0:r1], False)
         kernels.moe_combine(y, pair_row, self.top, out, accumulate)
 
 
