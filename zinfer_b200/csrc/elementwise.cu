@@ -193,6 +193,16 @@ template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ out, size_t total) {
   zk_let_next_start();
   zk_wait_prior();
+  if constexpr (sizeof(T) == 2) {
+    if (total % 4 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16) == 0) {
+      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total / 4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = reinterpret_cast<const float4*>(in)[i];
+        __nv_bfloat162 pk[2] = {__floats2bfloat162_rn(v.x, v.y), __floats2bfloat162_rn(v.z, v.w)};
+        reinterpret_cast<uint2*>(out)[i] = *reinterpret_cast<const uint2*>(pk);
+      }
+      return;
+    }
+  }
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
     out[i] = from_f32<T>(in[i]);
 }

@@ -14,6 +14,7 @@
 // experts (so that each expert's rows are one contiguous matrix for a tensor-core contraction) and the
 // weighted sum of a token's `top` result rows, added in the order of k.
 #include "common.cuh"
+#include <stdint.h>
 
 #define MOE_WARPS 8
 
@@ -171,6 +172,13 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
   const int t = row_token[blockIdx.x];       // < 0: a padding row
   const T* src = x + (size_t)(t < 0 ? 0 : t) * D;
   T* dst = xg + (size_t)blockIdx.x * D;
+  constexpr int PER = 16 / (int)sizeof(T);
+  if (D % PER == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xg)) % 16) == 0) {   // rows in 16-byte pieces
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int d = threadIdx.x; d < D / PER; d += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[d] = t < 0 ? zero : reinterpret_cast<const uint4*>(src)[d];
+    return;
+  }
   for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = t < 0 ? from_f32<T>(0.f) : src[d];
 }
 

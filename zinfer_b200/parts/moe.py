@@ -53,6 +53,10 @@ class TableMoE(FeedForward):
         self.table = self.table_host = self.w_gate_up = self.w_down = self.shared_gate = None
         self.interleave = FUSION_GROUP if ffn_dim % FUSION_GROUP == 0 else 0
         self.experts: list[SwiGLU] = []         # views of the stacked tensors, one ordinary feed-forward per expert
+        # pinned host buffer through which a prompt step's row tables reach the device, and the event of the
+        # copy that last read it: allocating pinned memory every step cost more than the step's kernels
+        self._staging: Optional[torch.Tensor] = None
+        self._staged: Optional[torch.cuda.Event] = None
 
     def parts(self):
         return [self.shared] if self.shared is not None else []
@@ -69,6 +73,7 @@ class TableMoE(FeedForward):
     def load(self, weights, dtype, device):
         self.table = weights[self.table_name].contiguous()
         self.table_host = self.table.cpu().numpy()
+        self._set_sort_keys()
         stack = (lambda g, u: interleave_rows([g, u])) if self.interleave else (lambda g, u: torch.cat([g, u], dim=0))
         self.w_gate_up = torch.stack([stack(weights[g], weights[u]) for g, u, _ in self.names]).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in self.names]).contiguous()
@@ -99,25 +104,49 @@ class TableMoE(FeedForward):
         self.shared.forward(ctx, rows, branch, False)
         kernels.gate_add(xn, self.shared_gate, branch, out)
 
+    def _set_sort_keys(self):
+        small = np.uint8 if self.n_experts <= 256 else (np.uint16 if self.n_experts <= 65536 else np.int64)
+        self.table_sort_keys = np.clip(self.table_host, 0, self.n_experts - 1).astype(small)
+
     def routing(self, host_tokens: np.ndarray, tile: int = 1):
         """For token ids known on the host: (row_token [rows]: the token of each row when the (token, k)
         pairs are sorted by expert, keeping their order within an expert, -1 for a padding row; pair_row
         [n * top]: the row pair t * top + k went to; bounds [experts + 1]: expert e owns rows bounds[e] ..
         bounds[e + 1]).  Every expert's rows are padded to a multiple of `tile`."""
-        ids = np.clip(np.asarray(host_tokens, dtype=np.int64), 0, self.vocab - 1)   # a bad id is flagged by the embedding
-        experts = np.clip(self.table_host[ids].reshape(-1), 0, self.n_experts - 1)
+        ids = np.asarray(host_tokens)
+        if ids.size and (ids.min() < 0 or ids.max() >= self.vocab):
+            ids = np.clip(ids, 0, self.vocab - 1)            # a bad id is flagged by the embedding kernel
+        experts = self.table_sort_keys[ids].reshape(-1)      # 8- or 16-bit keys: NumPy sorts those by radix, ten times faster
         order = np.argsort(experts, kind="stable")
         counts = np.bincount(experts, minlength=self.n_experts)
         padded = -(-counts // tile) * tile
-        bounds = np.concatenate([[0], np.cumsum(padded)])
-        starts = np.concatenate([[0], np.cumsum(counts)])[:-1]
-        sorted_experts = experts[order]
-        rows = bounds[sorted_experts] + (np.arange(order.size) - starts[sorted_experts])     # row of each sorted pair
+        bounds = np.zeros(self.n_experts + 1, dtype=np.int64)
+        np.cumsum(padded, out=bounds[1:])
+        starts = np.zeros(self.n_experts, dtype=np.int64)
+        np.cumsum(counts[:-1], out=starts[1:])
+        rows = np.arange(order.size) + np.repeat(bounds[:-1] - starts, counts)     # row of each pair, in sorted order
         row_token = np.full(int(bounds[-1]), -1, dtype=np.int32)
         row_token[rows] = order // self.top
         pair_row = np.empty(order.size, dtype=np.int32)
         pair_row[order] = rows
         return row_token, pair_row, bounds
+
+    def _upload(self, words: np.ndarray, device) -> torch.Tensor:
+        """int32 words on the device, copied through the part's own pinned buffer (rewritten only after the
+        copy that last read it has run)."""
+        n = int(words.size)
+        if self._staging is None or self._staging.numel() < n:
+            self._staging = torch.empty(max(n, 1024) * 2, dtype=torch.int32).pin_memory()
+            self._staged = None
+        if self._staged is not None:
+            self._staged.synchronize()
+        self._staging[:n].numpy()[:] = words
+        dev = torch.empty(n, dtype=torch.int32, device=device)
+        dev.copy_(self._staging[:n], non_blocking=True)
+        if self._staged is None:
+            self._staged = torch.cuda.Event()
+        self._staged.record()
+        return dev
 
     def _expert_by_expert(self, ctx, rows, host_tokens, out, accumulate):
         tile = kernels.GEMM_TC_GROUP_ROWS
@@ -129,7 +158,7 @@ class TableMoE(FeedForward):
             tile_group = np.repeat(np.arange(self.n_experts), np.diff(bounds) // tile).astype(np.int32) if grouped \
                 else np.zeros(0, dtype=np.int32)
             sizes = np.cumsum([row_token.size, pair_row.size, tile_group.size])
-            dev = torch.from_numpy(np.concatenate([row_token, pair_row, tile_group])).pin_memory().to(ctx.device, non_blocking=True)
+            dev = self._upload(np.concatenate([row_token, pair_row, tile_group]), ctx.device)
             return dev[:sizes[0]], dev[sizes[0]:sizes[1]], dev[sizes[1]:sizes[2]], bounds
 
         row_token, pair_row, tile_group, bounds = ctx.memo(("expert rows", id(self)), make)
