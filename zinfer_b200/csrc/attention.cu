@@ -196,61 +196,86 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 // The same step for a mixer whose q and k norms run over the WHOLE projection (all heads of a
 // token at once, weight of that width) and whose values may have another width than its keys;
 // no rotation.  A row of `qkv` holds [q (H * hd) | k (Hkv * hd) | v (Hkv * vd)], or q alone when
-// the call reads another call's cache (write_kv = 0).  One block per token; sums of squares are
-// float32 and added in an order that the thread layout alone fixes.
+// the call reads another call's cache (write_kv = 0).  Sums of squares are float32 and added in an
+// order that the thread layout alone fixes.
+#define SPAN_THREADS 256
+#define SPAN_KEEP 8       // values a thread keeps between the sum of squares and the scaling: rows of up to 2048
+
+// RMSNorm of one row of n values over its whole width (weight w, or none), written through `put(d, value)`.
+// Rows of up to SPAN_THREADS * SPAN_KEEP values are read once; the sum of squares is added per thread in
+// the order of its values and over the block in the order of the threads.
+template <typename T, typename Put>
+__device__ __forceinline__ void span_norm_row(const T* __restrict__ row, int n, const float* __restrict__ w, float eps,
+                                              float* scratch, Put put) {
+  const int tid = threadIdx.x;
+  float keep[SPAN_KEEP];
+  const bool fits = n <= SPAN_THREADS * SPAN_KEEP;
+  float ss = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < SPAN_KEEP; ++i) {
+      const int d = tid + i * SPAN_THREADS;
+      keep[i] = d < n ? to_f32(row[d]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < SPAN_KEEP; ++i) ss = fmaf(keep[i], keep[i], ss);
+  } else {
+    for (int d = tid; d < n; d += SPAN_THREADS) {
+      const float v = to_f32(row[d]);
+      ss = fmaf(v, v, ss);
+    }
+  }
+  float scale = 1.f;
+  if (w) {
+    ss = block_sum(ss, scratch);
+    scale = 1.0f / sqrtf(ss / (float)n + eps);
+  }
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < SPAN_KEEP; ++i) {
+      const int d = tid + i * SPAN_THREADS;
+      if (d < n) put(d, w ? (keep[i] * scale) * w[d] : keep[i]);
+    }
+  } else {
+    for (int d = tid; d < n; d += SPAN_THREADS) {
+      const float v = to_f32(row[d]);
+      put(d, w ? (v * scale) * w[d] : v);
+    }
+  }
+}
+
+// Block (t, 0) prepares the token's queries, block (t, 1) its keys and values (absent when write_kv = 0).
 template <typename T>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+__global__ void __launch_bounds__(SPAN_THREADS)
     qk_prepare_span_kernel(const T* __restrict__ qkv, int ld, T* __restrict__ q_out, T* __restrict__ k_cache,
                            T* __restrict__ v_cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
                            const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                            const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
-                           int Hkv, int hd, int vd, float eps, int page_size, int write_kv, int* status) {
+                           int Hkv, int hd, int vd, float eps, int page_size, int* status) {
   __shared__ float scratch[32];
   zk_let_next_start();
   zk_wait_prior();   // qkv is the kernel before's result
   const int t = blockIdx.x, tid = threadIdx.x;
   const int qd = H * hd, kd = Hkv * hd;
   const T* row = qkv + (size_t)t * ld;
-  float scale = 1.f;
-  if (q_w) {
-    float ss = 0.f;
-    for (int d = tid; d < qd; d += blockDim.x) {
-      const float v = to_f32(row[d]);
-      ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    scale = 1.0f / sqrtf(ss / (float)qd + eps);
+  if (blockIdx.y == 0) {
+    T* dst = q_out + (size_t)t * qd;
+    span_norm_row(row, qd, q_w, eps, scratch, [&](int d, float v) { dst[d] = from_f32<T>(v); });
+    return;
   }
-  for (int d = tid; d < qd; d += blockDim.x) {
-    const float v = to_f32(row[d]);
-    q_out[(size_t)t * qd + d] = from_f32<T>(q_w ? (v * scale) * q_w[d] : v);
-  }
-  if (!write_kv) return;
   const int pos = tok_pos[t];
   const int page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
   if (page < 0) {
     if (tid == 0) atomicExch(status, 2);
     return;
   }
-  const T* krow = row + qd;
-  float kscale = 1.f;
-  if (k_w) {
-    float ss = 0.f;
-    for (int d = tid; d < kd; d += blockDim.x) {
-      const float v = to_f32(krow[d]);
-      ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    kscale = 1.0f / sqrtf(ss / (float)kd + eps);
-  }
   const int in_page = pos % page_size;
-  for (int d = tid; d < kd; d += blockDim.x) {
-    const float v = to_f32(krow[d]);
+  span_norm_row(row + qd, kd, k_w, eps, scratch, [&](int d, float v) {
     const int kh = d / hd, e = d - kh * hd;
-    k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] = from_f32<T>(k_w ? (v * kscale) * k_w[d] : v);
-  }
-  const T* vrow = krow + kd;
-  for (int d = tid; d < Hkv * vd; d += blockDim.x) {
+    k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] = from_f32<T>(v);
+  });
+  const T* vrow = row + qd + kd;
+  for (int d = tid; d < Hkv * vd; d += SPAN_THREADS) {
     const int kh = d / vd, e = d - kh * vd;
     v_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * vd + e] = vrow[d];
   }
@@ -596,13 +621,13 @@ int zk_qk_prepare_span(const void* qkv, int ld, void* q_out, void* k_cache, void
   if (hd <= 0 || vd <= 0 || H <= 0 || Hkv <= 0 || page_size <= 0) return ZK_EINVAL;
   if (ld < H * hd + (write_kv ? Hkv * (hd + vd) : 0)) return ZK_EINVAL;
   if (dtype == ZK_F32)
-    return zk_launch_dependent(qk_prepare_span_kernel<float>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,
+    return zk_launch_dependent(qk_prepare_span_kernel<float>, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), 0, stream,
         (const float*)qkv, ld, (float*)q_out, (float*)k_cache, (float*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
-        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, write_kv, status);
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status);
   if (dtype == ZK_BF16)
-    return zk_launch_dependent(qk_prepare_span_kernel<bf16>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,
+    return zk_launch_dependent(qk_prepare_span_kernel<bf16>, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), 0, stream,
         (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
-        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, write_kv, status);
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status);
   return ZK_EINVAL;
 }
 

@@ -168,6 +168,43 @@ __global__ void rmsnorm_add_kernel(const float* __restrict__ m, const float* __r
   }
 }
 
+// The same with 16-byte loads and stores (dim a multiple of 4, at most 16 values per thread, aligned rows).
+__global__ void rmsnorm_add_vec4_kernel(const float* __restrict__ m, const float* __restrict__ w, float* __restrict__ x,
+                                        int dim, float eps) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int r = blockIdx.x;
+  const float4* mr = reinterpret_cast<const float4*>(m + (size_t)r * dim);
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)r * dim);
+  const int n4 = dim >> 2;
+  float4 v[4], xv[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    v[i] = d < n4 ? mr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    xv[i] = d < n4 ? xr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    ss = fmaf(v[i].x, v[i].x, ss);
+    ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss);
+    ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d >= n4) continue;
+    const float4 wv = reinterpret_cast<const float4*>(w)[d];
+    xr[d] = make_float4(xv[i].x + (v[i].x * scale) * wv.x, xv[i].y + (v[i].y * scale) * wv.y,
+                        xv[i].z + (v[i].z * scale) * wv.z, xv[i].w + (v[i].w * scale) * wv.w);
+  }
+}
+
 // Activations of a plain (ungated) feed-forward, float32 arithmetic:
 // 0 = gelu with erf: 0.5 z (1 + erf(z / sqrt 2)); 1 = gelu with tanh:
 // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2 = silu; 3 = relu.
@@ -238,12 +275,37 @@ __global__ void gate_add_kernel(const float* __restrict__ x, const float* __rest
   zk_wait_prior();
   const int t = blockIdx.x;
   const float* xr = x + (size_t)t * dim;
-  float dot = 0.f;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) dot = fmaf(xr[d], g[d], dot);
-  dot = block_sum(dot, scratch);
-  const float gate = 1.0f / (1.0f + expf(-dot));
   const float* sr = s + (size_t)t * out_dim;
   float* mr = m + (size_t)t * out_dim;
+  const bool vec = dim % 4 == 0 && out_dim % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(s) |
+                    reinterpret_cast<uintptr_t>(m)) % 16 == 0;
+  float dot = 0.f;
+  if (vec) {     // the same products, each thread adding its four in order
+    for (int d = threadIdx.x; d < dim / 4; d += blockDim.x) {
+      const float4 a = reinterpret_cast<const float4*>(xr)[d], b = reinterpret_cast<const float4*>(g)[d];
+      dot = fmaf(a.x, b.x, dot);
+      dot = fmaf(a.y, b.y, dot);
+      dot = fmaf(a.z, b.z, dot);
+      dot = fmaf(a.w, b.w, dot);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dot = fmaf(xr[d], g[d], dot);
+  }
+  dot = block_sum(dot, scratch);
+  const float gate = 1.0f / (1.0f + expf(-dot));
+  if (vec) {
+    for (int d = threadIdx.x; d < out_dim / 4; d += blockDim.x) {
+      const float4 a = reinterpret_cast<const float4*>(sr)[d];
+      float4 o = reinterpret_cast<float4*>(mr)[d];
+      o.x = fmaf(gate, a.x, o.x);
+      o.y = fmaf(gate, a.y, o.y);
+      o.z = fmaf(gate, a.z, o.z);
+      o.w = fmaf(gate, a.w, o.w);
+      reinterpret_cast<float4*>(mr)[d] = o;
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < out_dim; d += blockDim.x) mr[d] = fmaf(gate, sr[d], mr[d]);
 }
 
@@ -332,6 +394,11 @@ int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, flo
   if (dim <= 0) return ZK_EINVAL;
   int threads = 32;
   while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  const bool aligned = (reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) % 16 == 0;
+  if (dim % 4 == 0 && dim <= 16 * threads && aligned) {
+    while (threads > 32 && threads * 4 >= 2 * dim) threads >>= 1;   // no idle warps for short rows
+    return zk_launch_dependent(rmsnorm_add_vec4_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps);
+  }
   return zk_launch_dependent(rmsnorm_add_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps);
 }
 
