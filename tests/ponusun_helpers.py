@@ -70,6 +70,12 @@ CONFIGS = {
            "canon": {"taps": 1}, "logit_softcap": 5.0,
            "layers": [_layer(_mixer(2, 2, 24, 24, 0.2, 9), _moe(2, 2, 16, 8)),
                       _layer(_mixer(2, 2, 24, 24, 0.2, 9, kv_from=0), _moe(3, 1, 8))]},
+    # sizes that no vectorised or tensor-core kernel takes: a width that is no multiple of 4, odd head widths,
+    # five heads on five, a vocabulary that is prime, experts of 10 hidden units
+    "pf": {"architecture": "Ponusun", "vocab": 71, "width": 38, "max_positions": 150, "norm": {"eps": 1e-4},
+           "canon": {"taps": 6}, "logit_softcap": 20.0,
+           "layers": [_layer(_mixer(5, 5, 10, 6, 0.3, 14), _moe(3, 2, 10, 14)),
+                      _layer(_mixer(5, 5, 10, 6, 0.3, 30, kv_from=0), {"kind": "dense", "ff": 50})]},
 }
 
 

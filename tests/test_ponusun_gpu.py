@@ -85,7 +85,7 @@ def test_whole_prompts(zoo, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,cuts", [("pa", [30]), ("pb", [1]), ("pc", [77]), ("pe", [2]), ("pa", [2, 2, 5, 1, 17, 3, 2, 16, 16]),
-                                       ("pb", [64, 2, 30, 2]), ("pc", [3, 61, 64, 2]), ("pd", [5, 2])])
+                                       ("pb", [64, 2, 30, 2]), ("pc", [3, 61, 64, 2]), ("pd", [5, 2]), ("pf", [7, 2, 40])])
 def test_portions_and_single_tokens_give_what_the_whole_prompt_gives(zoo, name, dtype, cuts):
     """A sequence fed in portions (down to two tokens, across page borders) and then token by token, long
     enough for every window to pass over tokens that came one at a time."""

@@ -27,7 +27,7 @@ def parse_ids(text: str) -> list[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="zinfer_b200", description="LFM2 generation on one B200")
+    ap = argparse.ArgumentParser(prog="zinfer_b200", description="generation on one B200 (the model class is chosen by config.json)")
     ap.add_argument("-m", "--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("-p", "--prompt", help="prompt as token ids, comma or space separated")
     ap.add_argument("-f", "--file", help="file with one prompt (token ids) per line")

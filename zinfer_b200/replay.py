@@ -25,7 +25,8 @@ import numpy as np
 import torch
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
-TOKEN_UNIT = 64          # --max-tokens counts each request rounded up to this many tokens
+TOKEN_UNIT = 64          # tokens per cache page
+MAX_REQUESTS = 256       # requests alive at once (each holds a slot and may leave a page partly empty)
 
 
 def main(argv=None) -> int:
@@ -34,7 +35,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=sorted(DTYPES))
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time")
     args = ap.parse_args(argv)
 
     from .engine.engine import Engine
@@ -44,8 +45,11 @@ def main(argv=None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     dtype = DTYPES[args.dtype]
     model = load_model(args.model, dtype=dtype, device="cuda")
+    # Every live request holds at least one token, so there are at most --max-tokens of them; each may leave
+    # its last page partly empty, so the cache gets one page more per request than the tokens alone need.
     max_tokens = max(TOKEN_UNIT, -(-args.max_tokens // TOKEN_UNIT) * TOKEN_UNIT)
-    engine = Engine(model, max_batch=max_tokens // TOKEN_UNIT, max_seq_len=max_tokens, max_tokens=max_tokens,
+    requests = max(1, min(args.max_tokens, MAX_REQUESTS))
+    engine = Engine(model, max_batch=requests, max_seq_len=max_tokens, max_tokens=max_tokens + requests * TOKEN_UNIT,
                     page_size=TOKEN_UNIT)
     slot_of: dict[str, int] = {}
 
