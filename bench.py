@@ -235,9 +235,9 @@ def secondary_arm(args) -> dict:
 # are the same, and LFM2's SwiGLU is as wide as the experts one Ponusun token runs (top * ff + shared).
 PONUSUN_SIZES = {
     "w1024": dict(width=1024, layers=8, heads=16, kv=4, dim=64, window=512, experts=16, top=2, ff=1024, shared=1024,
-                  dense_ff=4096, vocab=32768, taps=4),
+                  dense_ff=4096, vocab=32768, taps=3),
     "w2048": dict(width=2048, layers=8, heads=32, kv=8, dim=64, window=1024, experts=16, top=2, ff=2048, shared=2048,
-                  dense_ff=8192, vocab=65536, taps=4),
+                  dense_ff=8192, vocab=65536, taps=3),
 }
 
 
@@ -253,7 +253,7 @@ def ponusun_config(sz: dict) -> dict:
                 "shared": {"ff": sz["shared"]}})
         layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Ponusun", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
-            "norm": {"eps": 1e-5}, "canon": {"taps": sz["taps"]}, "logit_softcap": 30.0, "layers": layers}
+            "norm": {"eps": 1e-5}, "canon": {"taps": sz["taps"]}, "logit_softcap": 20.0, "layers": layers}
 
 
 def lfm2_like(sz: dict) -> dict:

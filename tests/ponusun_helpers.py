@@ -58,9 +58,9 @@ CONFIGS = {
     # sizes in multiples of 16 and 64 (the shapes the tensor-core contractions and fused epilogues take),
     # four heads per key/value head, five taps, a window of exactly one page
     "pc": {"architecture": "Ponusun", "vocab": 512, "width": 128, "max_positions": 512, "norm": {"eps": 1e-5},
-           "canon": {"taps": 5}, "logit_softcap": 30.0,
-           "layers": [_layer(_mixer(8, 2, 64, 64, 0.125, 64), _moe(8, 2, 64, 64)),
-                      _layer(_mixer(8, 2, 64, 64, 0.125, 48, kv_from=0), {"kind": "dense", "ff": 256}),
+           "canon": {"taps": 5}, "logit_softcap": 24.0,
+           "layers": [_layer(_mixer(8, 2, 64, 64, 0.12, 64), _moe(8, 2, 64, 64)),
+                      _layer(_mixer(8, 2, 64, 64, 0.12, 48, kv_from=0), {"kind": "dense", "ff": 256}),
                       _layer(_mixer(4, 2, 64, 128, 0.1, 100), _moe(6, 2, 32, 96))]},
     # what the file does not mention does not exist: no convolution, no cap, no window, one layer, no feed-forward
     "pd": {"architecture": "Ponusun", "vocab": 50, "width": 32, "max_positions": 128, "norm": {"eps": 1e-5},

@@ -221,6 +221,19 @@ template <typename T>
 __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, int kind) {
   zk_let_next_start();
   zk_wait_prior();
+  constexpr int PER = 16 / (int)sizeof(T);      // values in 16 bytes
+  if (total % PER == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16) == 0) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total / PER; i += (size_t)gridDim.x * blockDim.x) {
+      const uint4 raw = reinterpret_cast<const uint4*>(in)[i];
+      const T* v = reinterpret_cast<const T*>(&raw);
+      uint4 packed;
+      T* o = reinterpret_cast<T*>(&packed);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) o[j] = from_f32<T>(zk_activate(to_f32(v[j]), kind));
+      reinterpret_cast<uint4*>(out)[i] = packed;
+    }
+    return;
+  }
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
     out[i] = from_f32<T>(zk_activate(to_f32(in[i]), kind));
 }
