@@ -300,7 +300,8 @@ def test_a_reader_of_another_calls_cache_with_a_window_of_its_own(k, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,F,E,top,shared,rows", [(40, 24, 5, 3, 40, 7), (64, 16, 3, 1, 0, 1), (128, 64, 8, 2, 64, 40),
-                                                  (72, 20, 4, 4, 12, 3), (256, 96, 6, 2, 32, 200)])
+                                                  (72, 20, 4, 4, 12, 3), (256, 96, 6, 2, 32, 200),
+                                                  (256, 128, 5, 2, 0, 200)])     # widths of whole 256-wide tiles: the persistent grouped form
 def test_table_routed_experts(k, dtype, D, F, E, top, shared, rows):
     from zinfer_b200.cache import CacheManager, CallCacheSpec
     from zinfer_b200.parts import SwiGLU, TableMoE

@@ -59,8 +59,8 @@ struct Params {
   const float* emit_w;
   bf16* emit_x;
   float* emit_ssq;
-  // Grouped products (normal mode, one tile per block): W is [groups, N, K] and the 128 rows of token tile t
-  // are multiplied with the matrix of group tile_group[t]; null = one matrix for all rows.
+  // Grouped products (normal mode; one tile per block, or persistent single blocks): W is [groups, N, K] and the
+  // 128 rows of token tile t are multiplied with the matrix of group tile_group[t]; null = one matrix for all rows.
   const int* tile_group;
 };
 
@@ -573,6 +573,10 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
     // for the kernel before and request the rows.
     const int pre = unit < n_tiles ? min(STAGES, nkb) : 0;
     const unsigned bar0 = PAIR ? cluster_addr(&full[0], 0) : 0u;   // stage s: bar0 + 8 s
+    // Grouped products (single blocks only): token tile a multiplies the matrix of group tile_group[a], whose
+    // rows start tile_group[a] * N further down.  The table is the step's own, so it is read after the wait.
+    const bool grouped = !PAIR && p.tile_group != nullptr;
+    if (grouped) zk_wait_prior();
     for (int s = 0; s < pre; ++s) {
       unsigned char* b_dst = tiles + (size_t)s * S::STAGE_BYTES + S::A_BYTES;
       const int b_tile = unit / tiles_m;
@@ -581,7 +585,7 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
         tma_load_2d_pair(b_dst, &map_b, s * BK, b_tile * BN + (int)rank * S::B_ROWS, bar0 + 8u * s);
       } else {
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        tma_load_2d(b_dst, &map_b, s * BK, b_tile * BN, &full[s]);
+        tma_load_2d(b_dst, &map_b, s * BK, b_tile * BN + (grouped ? p.tile_group[unit % tiles_m] * p.N : 0), &full[s]);
       }
     }
     zk_let_next_start();
@@ -595,6 +599,7 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
     int it = pre;
     for (int t = unit; t < n_tiles && !*aborted; t += n_units) {
       const int a_tile = t % tiles_m, b_tile = t / tiles_m;
+      const int group_row = grouped ? p.tile_group[a_tile] * p.N : 0;
       for (int kb = (t == unit ? pre : 0); kb < nkb; ++kb, ++it) {
         const int s = it % STAGES;
         if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
@@ -613,7 +618,7 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
         } else {
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, kb * BK, a_tile * BM, &full[s]);
-          tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN, &full[s]);
+          tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, b_tile * BN + group_row, &full[s]);
         }
       }
     }
@@ -949,8 +954,19 @@ int zk_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int 
   p.C = C; p.status = status;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = 1; p.swiglu = swiglu;
   p.tile_group = tile_group;
+  CUtensorMap ma, mb, mc;
+  const bool f32 = out_dtype == ZK_F32;
+  if (N % 256 == 0 && (ldc * (f32 ? 4 : 2)) % 16 == 0 && forced_form != 0) {
+    // persistent single blocks on 128 x 256 tiles, stores through the TMA (a matrix's rows end on a tile border)
+    constexpr int BW = 256;
+    if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, groups * N, K, K, BW) ||
+        !make_out_map(&mc, C, M, swiglu ? N / 2 : N, ldc, f32))
+      return ZK_EINVAL;
+    const int n_tiles = (M / BM) * (N / BW);
+    return f32 ? launch_persistent<BW, 4, false, float>(ma, mb, mc, p, n_tiles, stream)
+               : launch_persistent<BW, 4, false, bf16>(ma, mb, mc, p, n_tiles, stream);
+  }
   constexpr int BN = 128;
-  CUtensorMap ma, mb;
   if (!make_map(&ma, X, M, K, ldx, BM) || !make_map(&mb, W, groups * N, K, K, BN)) return ZK_EINVAL;
   dim3 grid(M / BM, ceil_div_i(N, BN), 1);
   return out_dtype == ZK_F32 ? launch<BN, 3, false, float>(ma, mb, p, grid, stream)
