@@ -34,7 +34,10 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                                   const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv,
                                   int hd, int n_rot, int interleaved, float eps, int page_size, int write_kv,
-                                  int* status) {
+                                  int* status, int vd, int unit_norm_after) {
+  // vd: width of a value head (a row of qkv is [q H*hd | k Hkv*hd | v Hkv*vd]).  unit_norm_after: q and k
+  // heads are divided by their root mean square (no weight) AFTER the rotation; q_w / k_w, if given,
+  // weigh an RMS norm BEFORE it.
   __shared__ float sm_all[ATT_WARPS][ATT_MAX_HD];
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -45,11 +48,14 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
   const int kind = s < H ? 0 : (s < H + Hkv ? 1 : 2);  // 0 q, 1 k, 2 v
   if (kind != 0 && !write_kv && !dense_out) return;
   float* sm = sm_all[warp];
-  const T* src = qkv + (size_t)t * slots * hd + (size_t)s * hd;
+  const size_t row_w = (size_t)(H + Hkv) * hd + (size_t)Hkv * vd;
+  const int wd = kind == 2 ? vd : hd;
+  const size_t col0 = kind == 2 ? (size_t)(H + Hkv) * hd + (size_t)(s - H - Hkv) * vd : (size_t)s * hd;
+  const T* src = qkv + (size_t)t * row_w + col0;
   const float* w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
 
   float ss = 0.f;
-  for (int d = lane; d < hd; d += 32) {
+  for (int d = lane; d < wd; d += 32) {
     const float v = to_f32(src[d]);
     sm[d] = v;
     ss = fmaf(v, v, ss);
@@ -74,9 +80,17 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     }
     __syncwarp();
   }
+  if (kind != 2 && unit_norm_after) {
+    float s2 = 0.f;
+    for (int d = lane; d < hd; d += 32) s2 = fmaf(sm[d], sm[d], s2);
+    s2 = warp_sum(s2);
+    const float scale = 1.0f / sqrtf(s2 / (float)hd + eps);
+    for (int d = lane; d < hd; d += 32) sm[d] *= scale;
+    __syncwarp();
+  }
   T* dst;
   if (dense_out) {
-    dst = dense_out + (size_t)t * slots * hd + (size_t)s * hd;
+    dst = dense_out + (size_t)t * row_w + col0;
   } else if (kind == 0) {
     dst = q_out + (size_t)t * H * hd + (size_t)s * hd;
   } else {
@@ -88,9 +102,9 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     }
     const int kh = kind == 1 ? s - H : s - H - Hkv;
     T* base = kind == 1 ? k_cache : v_cache;
-    dst = base + (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd;
+    dst = base + (((size_t)page * Hkv + kh) * page_size + pos % page_size) * wd;
   }
-  for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(sm[d]);
+  for (int d = lane; d < wd; d += 32) dst[d] = from_f32<T>(sm[d]);
 }
 
 // The same for prompt steps with head sizes 64 and 128 and a rotation over the whole head in
@@ -294,19 +308,25 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                     const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                     const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd,
                     int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
-                    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2) {
+                    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2, int cross) {
   // vd: width of a value row (the keys' width is hd); NPL covers vd.  bias_r1 / bias_r2 [H]: with both
   // given, r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query i and key j (float32).
+  // cross: every query head's weights are applied to the values of EVERY key/value head, one value head
+  // per block (blockIdx.y also counts them), and the unnormalised sums go to part_o / part_ml whatever
+  // num_splits is, rows ordered (split, token, head, value head): what a mix of the heads' weights
+  // after the softmax needs (attn_merge_talk_kernel).
   extern __shared__ float smem[];
   float* qs = smem;                               // [ATT_ROWS][hd]
   float* Ks = qs + ATT_ROWS * hd;                 // [ATT_TK][hd + 1]
   float* Vs = Ks + ATT_TK * (hd + 1);             // [ATT_TK][vd]
-  long long* rowoff = reinterpret_cast<long long*>(Vs + ATT_TK * vd + ((ATT_TK * (hd + 1) + ATT_TK * vd) & 1));  // [ATT_TK], 8-byte aligned
+  long long* rowoff = reinterpret_cast<long long*>(Vs + ATT_TK * vd + ((ATT_TK * (hd + 1) + ATT_TK * vd) & 1));  // [2][ATT_TK], 8-byte aligned
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = H / Hkv;
   const int chunks = (g + gc - 1) / gc;
-  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const int kvh = (blockIdx.y / chunks) % Hkv, chunk = blockIdx.y % chunks;
+  const int VH = cross ? Hkv : 1;
+  const int vh = cross ? blockIdx.y / (chunks * Hkv) : kvh;      // the key/value head whose values this block reads
   const int b = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
   const int split = blockIdx.z;
   const int t_base = cu_q[b], Tq = cu_q[b + 1] - t_base;
@@ -377,6 +397,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
         if (page >= 0) off = ((long long)page * Hkv + kvh) * page_size + kp % page_size;   // row index; x hd or vd below
       }
       rowoff[tid] = off;
+      rowoff[ATT_TK + tid] = off < 0 ? off : off + (long long)(vh - kvh) * page_size;      // the value row
     }
     __syncthreads();
     for (int idx = tid; idx < ATT_TK * hd; idx += ATT_WARPS * 32) {
@@ -386,7 +407,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     }
     for (int idx = tid; idx < ATT_TK * vd; idx += ATT_WARPS * 32) {
       const int j = idx / vd, d = idx - j * vd;
-      const long long off = rowoff[j];
+      const long long off = rowoff[ATT_TK + j];
       Vs[j * vd + d] = off >= 0 ? to_f32(v_cache[off * vd + d]) : 0.f;
     }
     __syncthreads();
@@ -441,7 +462,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (!row_ok[i]) continue;
-    if (num_splits == 1) {
+    if (num_splits == 1 && !cross) {
       const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
       T* dst = out + (size_t)row_t[i] * H * vd + (size_t)row_h[i] * vd;
 #pragma unroll
@@ -450,7 +471,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
         if (d < vd) dst[d] = from_f32<T>(o[i][c] * inv);
       }
     } else {
-      const size_t row = ((size_t)split * n_tokens + row_t[i]) * H + row_h[i];
+      const size_t row = (((size_t)split * n_tokens + row_t[i]) * H + row_h[i]) * VH + (cross ? vh : 0);
       float* dst = part_o + row * vd;
 #pragma unroll
       for (int c = 0; c < NPL; ++c) {
@@ -519,10 +540,56 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     if (lane + 32 * i < hd) out[(size_t)row * hd + lane + 32 * i] = from_f32<T>(acc[i] * inv);
 }
 
+// (3b) merge for weights that are mixed across the heads after the softmax: with w_g(i, j) head g's softmax
+// weights and T [H, H],   out[t, h, :] = sum_g T[h, g] * (sum_j w_g(t, j) v_{kv(h)}(j, :)).
+// The inner sums are what the cross mode of attn_fwd_kernel left unnormalised per (split, token, head g,
+// value head): merged over the splits as in attn_merge_kernel, then weighed and added in the order of g.
+// One warp per (token, head h); float32 until the store.
+template <typename T>
+__global__ void attn_merge_talk_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const float* __restrict__ talk, T* __restrict__ out, int n_tokens, int H, int Hkv,
+                                       int vd, int num_splits) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)n_tokens * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const int c = h / (H / Hkv);
+  const size_t rows_per_split = (size_t)n_tokens * H * Hkv;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int g = 0; g < H; ++g) {
+    const size_t row = ((size_t)t * H + g) * Hkv + c;
+    float M = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[((size_t)s * rows_per_split + row) * 2]);
+    float L = 0.f, og[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) og[i] = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const size_t r = (size_t)s * rows_per_split + row;
+      const float ms = part_ml[r * 2];
+      if (ms == -INFINITY) continue;
+      const float e = expf(ms - M);
+      L = fmaf(e, part_ml[r * 2 + 1], L);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (lane + 32 * i < vd) og[i] = fmaf(e, part_o[r * vd + lane + 32 * i], og[i]);
+    }
+    const float wgt = L > 0.f ? talk[h * H + g] / L : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(wgt, og[i], acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (lane + 32 * i < vd) out[((size_t)t * H + h) * vd + lane + 32 * i] = from_f32<T>(acc[i]);
+}
+
 namespace {
 
 size_t attn_smem_bytes(int hd, int vd) {
-  return sizeof(float) * ((size_t)ATT_ROWS * hd + (size_t)ATT_TK * (hd + 1) + (size_t)ATT_TK * vd + 1) + sizeof(long long) * ATT_TK + 16;
+  return sizeof(float) * ((size_t)ATT_ROWS * hd + (size_t)ATT_TK * (hd + 1) + (size_t)ATT_TK * vd + 1) + sizeof(long long) * 2 * ATT_TK + 16;
 }
 
 template <typename T, int NPL>
@@ -530,7 +597,7 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd, const float* r1,
-                const float* r2, cudaStream_t stream) {
+                const float* r2, int cross, cudaStream_t stream) {
   const size_t smem = attn_smem_bytes(hd, vd);
   auto kern = attn_fwd_kernel<T, NPL>;
   if (smem > 48 * 1024) {
@@ -539,11 +606,11 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
   }
   const int g = H / Hkv;
   const int chunks = (g + gc - 1) / gc;
-  dim3 grid(n_tiles, Hkv * chunks, num_splits);
+  dim3 grid(n_tiles, Hkv * chunks * (cross ? Hkv : 1), num_splits);
   kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_o,
                                                part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
                                                pt_stride, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,
-                                               num_splits, split_keys, vd, r1, r2);
+                                               num_splits, split_keys, vd, r1, r2, cross);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -552,12 +619,12 @@ int dispatch_attn(int hd, const void* q, const void* k_cache, const void* v_cach
                   float* part_ml, const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start,
                   const int* seq_slot, const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv,
                   int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
-                  const float* r1, const float* r2, cudaStream_t stream) {
+                  const float* r1, const float* r2, int cross, cudaStream_t stream) {
 #define ZK_ATT_CASE(N)                                                                                               \
   case N:                                                                                                            \
     return launch_attn<T, N>(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, \
                              page_table, pt_stride, n_tiles, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,  \
-                             num_splits, split_keys, vd, r1, r2, stream);
+                             num_splits, split_keys, vd, r1, r2, cross, stream);
   switch ((vd + 31) / 32) {
     ZK_ATT_CASE(1) ZK_ATT_CASE(2) ZK_ATT_CASE(3) ZK_ATT_CASE(4) ZK_ATT_CASE(5) ZK_ATT_CASE(6) ZK_ATT_CASE(7)
     ZK_ATT_CASE(8)
@@ -578,12 +645,15 @@ int zk_attn_max_head_dim() { return ATT_MAX_HD; }
 int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, void* v_cache, const float* q_w, const float* k_w,
                   const float* inv_freq, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                   const int* page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd, int n_rot,
-                  int interleaved, float eps, int page_size, int write_kv, int dtype, int* status,
-                  cudaStream_t stream) {
+                  int interleaved, float eps, int page_size, int write_kv, int dtype, int* status, int vd,
+                  int unit_norm_after, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || n_rot > hd || (n_rot & 1) || page_size <= 0) return ZK_EINVAL;
+  if (vd <= 0) vd = hd;
+  if (vd > ATT_MAX_HD) return ZK_EINVAL;
   // many tokens, whole-head half-split rotation (or none): one block per token
-  if (n_tokens >= 256 && !dense_out && (hd == 64 || hd == 128) && (!inv_freq || (n_rot == hd && !interleaved)) &&
+  if (n_tokens >= 256 && !dense_out && (hd == 64 || hd == 128) && vd == hd && !unit_norm_after &&
+      (!inv_freq || (n_rot == hd && !interleaved)) &&
       (dtype == ZK_F32 || dtype == ZK_BF16)) {
 #define ZK_QKP(T, HDV)                                                                                               \
   zk_launch_dependent(qk_prepare_token_kernel<T, HDV>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,             \
@@ -601,11 +671,13 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
   if (dtype == ZK_F32)
     return zk_launch_dependent(qk_prepare_kernel<float>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const float*)qkv, (float*)q_out, (float*)dense_out, (float*)k_cache, (float*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos,
-        seq_slot, page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status);
+        seq_slot, page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status, vd,
+        unit_norm_after);
   else if (dtype == ZK_BF16)
     return zk_launch_dependent(qk_prepare_kernel<bf16>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const bf16*)qkv, (bf16*)q_out, (bf16*)dense_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot,
-        page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status);
+        page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status, vd,
+        unit_norm_after);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
@@ -637,8 +709,9 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int dtype, int vd,
-                const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
+                const float* bias_r1, const float* bias_r2, int cross, cudaStream_t stream) {
   if (n_tiles <= 0 || n_tokens <= 0) return 0;
+  if (cross && (!part_o || !part_ml)) return ZK_EINVAL;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0) return ZK_EINVAL;
   if (vd <= 0 || vd > ATT_MAX_HD || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
   if (gc <= 0 || gc > ATT_ROWS || bq <= 0 || bq * gc > ATT_ROWS || num_splits < 1) return ZK_EINVAL;
@@ -646,11 +719,29 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
   if (dtype == ZK_F32)
     return dispatch_attn<float>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                 seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale,
-                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, stream);
+                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, stream);
   if (dtype == ZK_BF16)
     return dispatch_attn<bf16>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale, bq,
-                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, stream);
+                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, stream);
+  return ZK_EINVAL;
+}
+
+// part_o [num_splits, n_tokens*H*Hkv, vd], part_ml [num_splits, n_tokens*H*Hkv, 2] as the cross mode of zk_attn_fwd
+// leaves them; talk float32 [H, H]; out [n_tokens, H*vd].
+int zk_attn_merge_talk(const float* part_o, const float* part_ml, const float* talk, void* out, int n_tokens, int H, int Hkv,
+                       int vd, int num_splits, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || Hkv <= 0 || H % Hkv || vd <= 0 || vd > ATT_MAX_HD || num_splits < 1 || !talk) return ZK_EINVAL;
+  const int warps = 4;
+  const long long items = (long long)n_tokens * H;
+  const int blocks = (int)((items + warps - 1) / warps);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(attn_merge_talk_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, talk,
+                               (float*)out, n_tokens, H, Hkv, vd, num_splits);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(attn_merge_talk_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, talk,
+                               (bf16*)out, n_tokens, H, Hkv, vd, num_splits);
   return ZK_EINVAL;
 }
 

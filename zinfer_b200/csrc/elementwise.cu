@@ -207,12 +207,16 @@ __global__ void rmsnorm_add_vec4_kernel(const float* __restrict__ m, const float
 
 // Activations of a plain (ungated) feed-forward, float32 arithmetic:
 // 0 = gelu with erf: 0.5 z (1 + erf(z / sqrt 2)); 1 = gelu with tanh:
-// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2 = silu; 3 = relu.
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2 = silu; 3 = relu; 4 = the square of relu.
 __device__ __forceinline__ float zk_activate(float z, int kind) {
   switch (kind) {
     case 0: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
     case 1: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
     case 2: return z / (1.0f + expf(-z));
+    case 4: {
+      const float r = fmaxf(z, 0.f);
+      return r * r;
+    }
     default: return fmaxf(z, 0.f);
   }
 }
@@ -277,6 +281,100 @@ __global__ void weighted_sum_kernel(const float* __restrict__ planes, const floa
     for (int j = 1; j < n_terms; ++j) acc = fmaf(w[j], planes[(size_t)j * plane + i], acc);
     out[i] = acc;
   }
+}
+
+// x[t, c] += s[c] * m[t, c]: a sublayer's result m summed into the residual rows through a learned
+// scale per channel.  Float32; the product is rounded before the sum (no fused multiply-add), so the
+// row is the same whether the scale was applied here or by the kernel that produced m.
+__global__ void scale_add_kernel(const float* __restrict__ m, const float* __restrict__ s, float* __restrict__ x,
+                                 size_t total, int dim) {
+  zk_let_next_start();
+  zk_wait_prior();
+  if (dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(x)) % 16) == 0) {
+    const int d4 = dim >> 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total / 4; i += (size_t)gridDim.x * blockDim.x) {
+      const float4 a = reinterpret_cast<const float4*>(m)[i], w = reinterpret_cast<const float4*>(s)[i % d4];
+      float4 v = reinterpret_cast<float4*>(x)[i];
+      v.x = __fadd_rn(v.x, __fmul_rn(w.x, a.x));
+      v.y = __fadd_rn(v.y, __fmul_rn(w.y, a.y));
+      v.z = __fadd_rn(v.z, __fmul_rn(w.z, a.z));
+      v.w = __fadd_rn(v.w, __fmul_rn(w.w, a.w));
+      reinterpret_cast<float4*>(x)[i] = v;
+    }
+    return;
+  }
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = __fadd_rn(x[i], __fmul_rn(s[i % dim], m[i]));
+}
+
+// x[t, :] = (x[t, :] + base[t, :]) + vec[:]  (base may be absent): what a repeated stretch of layers is
+// given before each of its passes, the rows as they left the embedding and a learned vector per pass.
+__global__ void rows_add_kernel(float* __restrict__ x, const float* __restrict__ base, const float* __restrict__ vec,
+                                size_t total, int dim) {
+  zk_let_next_start();
+  zk_wait_prior();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = x[i];
+    if (base) v += base[i];
+    x[i] = v + vec[i % dim];
+  }
+}
+
+// Token shift on normalised rows: n_t = rms(x_t) * w (or x_t itself without w), h_t = n_t + (n_{t-1} - n_t) * mu,
+// with n_{t-1} the sequence's previous token's n: the row before in the packed batch, or, for the first
+// token a sequence brings in this step, the row `state[slot]` that the step before left (zeros at a
+// sequence's start).  One block per token; float32 throughout, h in the run dtype.  n_{t-1} is computed
+// again from x_{t-1} with the arithmetic that wrote the state, so a cut between two steps changes no bit.
+// With `write_state` (steps of one token per sequence) the block also leaves n_t as the new state;
+// otherwise norm_shift_state_kernel does, after every block has read the old one.
+__device__ __forceinline__ float row_scale(const float* __restrict__ xr, int dim, float eps, float* scratch) {
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
+  ss = block_sum(ss, scratch);
+  return 1.0f / sqrtf(ss / (float)dim + eps);
+}
+
+template <typename TO>
+__global__ void norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ mu,
+                                  float* __restrict__ state, long long state_stride, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, TO* __restrict__ h,
+                                  int dim, float eps, int write_state) {
+  __shared__ float scratch[2][32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x;
+  const int b = tok_seq[t];
+  const bool first = t == cu_q[b];
+  const float* xr = x + (size_t)t * dim;
+  const float* xp = first ? nullptr : xr - dim;
+  float* st = state + (size_t)seq_slot[b] * state_stride;
+  float sc = 1.f, sp = 1.f;
+  if (w) {
+    sc = row_scale(xr, dim, eps, scratch[0]);
+    if (xp) sp = row_scale(xp, dim, eps, scratch[1]);
+  }
+  TO* hr = h + (size_t)t * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float n = w ? (xr[d] * sc) * w[d] : xr[d];
+    const float p = xp ? (w ? (xp[d] * sp) * w[d] : xp[d]) : st[d];
+    hr[d] = from_f32<TO>(n + (p - n) * mu[d]);
+    if (write_state) st[d] = n;
+  }
+}
+
+__global__ void norm_shift_state_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ state,
+                                        long long state_stride, const int* __restrict__ cu_q,
+                                        const int* __restrict__ seq_slot, int dim, float eps) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int b = blockIdx.x;
+  const int t = cu_q[b + 1] - 1;
+  if (t < cu_q[b]) return;
+  const float* xr = x + (size_t)t * dim;
+  float* st = state + (size_t)seq_slot[b] * state_stride;
+  const float sc = w ? row_scale(xr, dim, eps, scratch) : 1.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) st[d] = w ? (xr[d] * sc) * w[d] : xr[d];
 }
 
 // m[t, :] += sigmoid(x[t, :] . g) * s[t, :]: a branch s that every token takes, weighed by one
@@ -417,7 +515,7 @@ int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, flo
 
 int zk_activation(const void* in, void* out, long long total, int kind, int dtype, cudaStream_t stream) {
   if (total <= 0) return 0;
-  if (kind < 0 || kind > 3) return ZK_EINVAL;
+  if (kind < 0 || kind > 4) return ZK_EINVAL;
   const int threads = 256, blocks = grid_for_total((size_t)total, threads);
   if (dtype == ZK_F32)
     return zk_launch_dependent(activation_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, (size_t)total, kind);
@@ -448,6 +546,43 @@ int zk_weighted_sum(const float* planes, const float* w, int n_terms, long long 
   if (n_terms < 1 || (n_terms > 1 && !w)) return ZK_EINVAL;
   const int threads = 256, blocks = grid_for_total((size_t)plane, threads);
   return zk_launch_dependent(weighted_sum_kernel, dim3(blocks), dim3(threads), 0, stream, planes, w, n_terms, (size_t)plane, out);
+}
+
+int zk_scale_add(const float* m, const float* s, float* x, long long total, int dim, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (dim <= 0 || total % dim) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)total / (dim % 4 == 0 ? 4 : 1), threads);
+  return zk_launch_dependent(scale_add_kernel, dim3(blocks), dim3(threads), 0, stream, m, s, x, (size_t)total, dim);
+}
+
+int zk_rows_add(float* x, const float* base, const float* vec, long long total, int dim, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (dim <= 0 || total % dim || !vec) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)total, threads);
+  return zk_launch_dependent(rows_add_kernel, dim3(blocks), dim3(threads), 0, stream, x, base, vec, (size_t)total, dim);
+}
+
+// Token shift (see norm_shift_kernel).  x float32 [n, dim]; w [dim] or null; mu [dim]; state rows
+// `state_stride` floats apart, one per slot; h [n, dim] in out_dtype.
+int zk_norm_shift(const float* x, const float* w, const float* mu, float* state, long long state_stride,
+                  const int* tok_seq, const int* cu_q, const int* seq_slot, void* h, int n, int n_seqs, int dim, float eps,
+                  int single_token, int out_dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim <= 0 || n_seqs <= 0 || !mu || !state) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  int rc;
+  if (out_dtype == ZK_F32)
+    rc = zk_launch_dependent(norm_shift_kernel<float>, dim3(n), dim3(threads), 0, stream, x, w, mu, state, state_stride,
+                             tok_seq, cu_q, seq_slot, (float*)h, dim, eps, single_token ? 1 : 0);
+  else if (out_dtype == ZK_BF16)
+    rc = zk_launch_dependent(norm_shift_kernel<bf16>, dim3(n), dim3(threads), 0, stream, x, w, mu, state, state_stride,
+                             tok_seq, cu_q, seq_slot, (bf16*)h, dim, eps, single_token ? 1 : 0);
+  else
+    return ZK_EINVAL;
+  if (rc != 0 || single_token) return rc;
+  return zk_launch_dependent(norm_shift_state_kernel, dim3(n_seqs), dim3(threads), 0, stream, x, w, state, state_stride,
+                             cu_q, seq_slot, dim, eps);
 }
 
 int zk_gate_add(const float* x, const float* g, const float* s, float* m, int n, int dim, int out_dim, cudaStream_t stream) {

@@ -34,6 +34,13 @@ _SIGNATURES = {
         "zk_softcap": "plfp",
         "zk_weighted_sum": "ppilpp",
         "zk_gate_add": "ppppiiip",
+        "zk_scale_add": "ppplip",
+        "zk_rows_add": "ppplip",
+        "zk_norm_shift": "pppplppppiiifiip",
+    },
+    "hgrn2": {
+        "zk_hgrn2_scan": "pippplpppiiiip",
+        "zk_hgrn2_max_dim": "",
     },
     "seqconv": {
         "zk_seqconv_forward": "ppppppp" + "iiiliiip",
@@ -96,9 +103,10 @@ _SIGNATURES = {
         "zk_sample": "piififfffip" + "lpp" + "pp",
     },
     "attention": {
-        "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiipp",
+        "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiip" + "ii" + "p",
         "zk_qk_prepare_span": "pipppppppppiiiiiifiiipp",
-        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ipp" + "p",
+        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ippi" + "p",
+        "zk_attn_merge_talk": "ppppiiiiiip",
         "zk_attn_merge": "pppiiiip",
         "zk_attn_rows_per_block": "",
         "zk_attn_max_head_dim": "",
@@ -240,7 +248,7 @@ def rmsnorm_add(m: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tens
     return x
 
 
-ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu_squared": 4}
 
 
 def activation(z: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -301,6 +309,77 @@ def gate_add(x: torch.Tensor, gate: torch.Tensor, branch: torch.Tensor, m: torch
     _check(_fn("elementwise", "zk_gate_add")(_ptr(x), _ptr(gate), _ptr(branch), _ptr(m), n, D, m.shape[1], _stream()),
            "gate_add")
     return m
+
+
+def scale_add(m: torch.Tensor, scale: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """x[t, c] += scale[c] * m[t, c], all float32: a sublayer's result summed into the residual rows through a
+    learned scale per channel."""
+    _need(m, "m", torch.float32, (None, None))
+    _need(x, "x", torch.float32, tuple(m.shape))
+    _need(scale, "scale", torch.float32, (m.shape[1],))
+    _check(_fn("elementwise", "zk_scale_add")(_ptr(m), _ptr(scale), _ptr(x), m.numel(), m.shape[1], _stream()), "scale_add")
+    return x
+
+
+def rows_add(x: torch.Tensor, vec: torch.Tensor, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[t, :] = (x[t, :] + base[t, :]) + vec[:] in place (without `base`: x[t, :] += vec), float32."""
+    _need(x, "x", torch.float32, (None, None))
+    _need(vec, "vec", torch.float32, (x.shape[1],))
+    if base is not None:
+        _need(base, "base", torch.float32, tuple(x.shape))
+    _check(_fn("elementwise", "zk_rows_add")(_ptr(x), _ptr(base), _ptr(vec), x.numel(), x.shape[1], _stream()), "rows_add")
+    return x
+
+
+def norm_shift(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, mu: torch.Tensor, state: torch.Tensor,
+               tok_seq, cu_q, seq_slot, n_seqs: int, out_dtype: torch.dtype, single_token: bool = False) -> torch.Tensor:
+    """Token shift of (optionally RMS-normalised) rows: n_t = rms(x_t) * weight (x_t itself without a weight),
+    h_t = n_t + (n_prev - n_t) * mu with n_prev the n of the sequence's token before, taken from the step's own
+    rows or, for the first token a sequence brings, from `state` [slots, >= D] (float32, a row per slot,
+    rows `state.stride(0)` apart), which afterwards holds the n of each sequence's last token.
+    x float32 [n, D] packed; h [n, D] in `out_dtype`."""
+    _need(x, "x", torch.float32, (None, None))
+    n, D = x.shape
+    if weight is not None:
+        _need(weight, "weight", torch.float32, (D,))
+    _need(mu, "mu", torch.float32, (D,))
+    _need(state, "state", torch.float32, contiguous=False)
+    if state.dim() != 2 or state.shape[1] < D or state.stride(1) != 1:
+        raise KernelError(f"norm_shift: state {tuple(state.shape)} must hold a row of {D} values per slot")
+    for t, nm in ((tok_seq, "tok_seq"), (cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    h = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "zk_norm_shift")(_ptr(x), _ptr(weight), _ptr(mu), _ptr(state), state.stride(0), _ptr(tok_seq),
+                                               _ptr(cu_q), _ptr(seq_slot), _ptr(h), n, n_seqs, D, eps,
+                                               1 if single_token else 0, dtype_code(out_dtype), _stream()), "norm_shift")
+    return h
+
+
+# ------------------------------------------------------------------------------- gated linear recurrence
+
+def hgrn2_max_dim() -> int:
+    return _constant("hgrn2", "zk_hgrn2_max_dim")
+
+
+def hgrn2_scan(qfv: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, cu_q, seq_slot,
+               n_seqs: int, n_heads: int, dim: int, value_dim: int) -> torch.Tensor:
+    """Per head S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t over each sequence's tokens, from the state
+    the step before left to the state this one leaves.  qfv float32 [n, 2*H*d + H*e], a row [q | f | v] as the
+    projections gave them (q <- silu, f <- lower + (1 - lower) * sigmoid(f + f_bias) here); state float32
+    [slots, H*d*e] (rows `state.stride(0)` apart), a slot's values ordered [H, d, e]; returns o float32 [n, H*e]."""
+    H, d, e = n_heads, dim, value_dim
+    _need(qfv, "qfv", torch.float32, (None, 2 * H * d + H * e))
+    _need(f_bias, "f_bias", torch.float32, (H * d,))
+    _need(lower, "lower", torch.float32, (H * d,))
+    _need(state, "state", torch.float32, contiguous=False)
+    if state.dim() != 2 or state.shape[1] != H * d * e or state.stride(1) != 1:
+        raise KernelError(f"hgrn2_scan: state {tuple(state.shape)} must hold {H * d * e} values per slot")
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    o = torch.empty((qfv.shape[0], H * e), dtype=torch.float32, device=qfv.device)
+    _check(_fn("hgrn2", "zk_hgrn2_scan")(_ptr(qfv), qfv.stride(0), _ptr(f_bias), _ptr(lower), _ptr(state), state.stride(0),
+                                         _ptr(o), _ptr(cu_q), _ptr(seq_slot), n_seqs, H, d, e, _stream()), "hgrn2_scan")
+    return o
 
 
 # ------------------------------------------------------------------------------- convolution over time on a mixer's input
@@ -801,14 +880,17 @@ def attn_max_head_dim() -> int:
 
 
 def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, n_heads: int,
-               n_kv: int, head_dim: int, n_rot: int, interleaved: bool, eps: float, status, write_kv: bool = True):
+               n_kv: int, head_dim: int, n_rot: int, interleaved: bool, eps: float, status, write_kv: bool = True,
+               value_dim: Optional[int] = None, unit_norm_after: bool = False):
     """Per-head RMSNorm of q and k (if weights are given), rotary encoding (if `inv_freq` is
-    given), q out as [n, H*hd], and k, v written to their pages.  k_cache / v_cache are one
-    layer's [pages, Hkv, page_size, hd]."""
-    _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, (n_heads + 2 * n_kv) * head_dim))
+    given), then with `unit_norm_after` q and k heads divided by their root mean square (no weight);
+    q out as [n, H*hd], and k, v written to their pages.  k_cache is one layer's
+    [pages, Hkv, page_size, hd], v_cache [pages, Hkv, page_size, value_dim (default hd)]."""
+    vd = head_dim if value_dim is None else int(value_dim)
+    _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, (n_heads + n_kv) * head_dim + n_kv * vd))
     n = qkv.shape[0]
-    for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
-        _need(c, nm, qkv.dtype, (None, n_kv, None, head_dim))
+    _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, None, head_dim))
+    _need(v_cache, "v_cache", qkv.dtype, (None, n_kv, None, vd))
     page_size = k_cache.shape[2]
     if head_dim % 2 or head_dim > attn_max_head_dim():
         raise KernelError(f"qk_prepare: head_dim {head_dim} must be even and <= {attn_max_head_dim()}")
@@ -822,7 +904,8 @@ def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_
     _check(_fn("attention", "zk_qk_prepare")(
         _ptr(qkv), _ptr(q), None, _ptr(k_cache), _ptr(v_cache), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _ptr(tok_seq),
         _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, n_rot,
-        1 if interleaved else 0, eps, page_size, 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), _stream()),
+        1 if interleaved else 0, eps, page_size, 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), vd,
+        1 if unit_norm_after else 0, _stream()),
         "qk_prepare")
     return q
 
@@ -862,7 +945,7 @@ def qk_normed(qkv, q_w, k_w, n_heads: int, n_kv: int, head_dim: int, eps: float,
     dense = torch.empty_like(qkv)
     _check(_fn("attention", "zk_qk_prepare")(
         _ptr(qkv), None, _ptr(dense), None, None, _ptr(q_w), _ptr(k_w), None, None, _ptr(tok_pos), None, None, 0,
-        qkv.shape[0], n_heads, n_kv, head_dim, 0, 0, eps, 1, 0, dtype_code(qkv.dtype), _ptr(status), _stream()),
+        qkv.shape[0], n_heads, n_kv, head_dim, 0, 0, eps, 1, 0, dtype_code(qkv.dtype), _ptr(status), head_dim, 0, _stream()),
         "qk_normed")
     return dense
 
@@ -896,13 +979,14 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 @functools.lru_cache(maxsize=None)      # a pure function of sizes, asked for by every attention layer of every step
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool, window: int = 0, value_dim: Optional[int] = None,
-                   biased: bool = False) -> tuple[str, int]:
+                   biased: bool = False, talking: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
-    taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc")."""
+    taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
+    are mixed across the heads after the softmax (`talking`) by the general kernel."""
     same_width = value_dim is None or value_dim == head_dim
-    if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
+    if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0 and not talking:
         if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
@@ -918,7 +1002,7 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
 def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
               head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
               single_token: bool = False, kind: Optional[str] = None, value_dim: Optional[int] = None,
-              bias: Optional[tuple] = None) -> torch.Tensor:
+              bias: Optional[tuple] = None, talk: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal grouped-query attention of a packed batch against the paged cache.  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
@@ -926,7 +1010,10 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     `attention_plan` chose it (the tile table must then have that plan's tokens per tile);
     without it the general kernel or the single-token kernel runs.  `value_dim`: width of a value
     row if it is not head_dim.  `bias` = (r1, r2), float32 [H] each: r1_h * ln(1 + r2_h * (i - j)) is taken
-    off the scaled score of query position i and key position j.  Both are the general kernel's."""
+    off the scaled score of query position i and key position j.  Both are the general kernel's.
+    `talk` float32 [H, H]: after the softmax head h's weights become sum_g talk[h, g] * (head g's weights), and
+    head h applies them to the values of its own key/value head (general kernel: every head's weights meet
+    every key/value head's values, and a merge kernel mixes the results)."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
     vd = head_dim if value_dim is None else int(value_dim)
@@ -935,6 +1022,10 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     if bias is not None:
         for b, nm in zip(bias, ("bias r1", "bias r2")):
             _need(b, nm, torch.float32, (n_heads,))
+    if talk is not None:
+        _need(talk, "talk", torch.float32, (n_heads, n_heads))
+        if kind not in (None, "general"):
+            raise KernelError(f"attention: the '{kind}' kernel mixes no weights across heads")
     if vd != head_dim and kind not in (None, "general"):
         raise KernelError(f"attention: the '{kind}' kernel takes no value width of its own")
     if bias is not None and kind not in (None, "general", "prompt_tc", "single_token_tc"):
@@ -950,12 +1041,13 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     bq, gc = attn_tile_shape(n_heads, n_kv)
     n_tiles = tile_seq.numel()
     out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
-    if vd != head_dim or (bias is not None and kind != "single_token_tc"):
+    if vd != head_dim or talk is not None or (bias is not None and kind != "single_token_tc"):
         single_token = False        # the general kernel runs single tokens as tiles of one query
     part_o = part_ml = None
-    if num_splits > 1:
-        part_o = torch.empty((num_splits, n * n_heads, vd), dtype=torch.float32, device=q.device)
-        part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
+    value_heads = n_kv if talk is not None else 1
+    if num_splits > 1 or talk is not None:
+        part_o = torch.empty((num_splits, n * n_heads * value_heads, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((num_splits, n * n_heads * value_heads, 2), dtype=torch.float32, device=q.device)
     if kind == "prompt_tc5":
         if (q.dtype != torch.bfloat16 or window > 0 or not k_cache.is_contiguous() or not v_cache.is_contiguous()
                 or not q.is_contiguous()
@@ -1001,8 +1093,13 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     _check(_fn("attention", "zk_attn_fwd")(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
-        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd, r1, r2, _stream()),
+        head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd, r1, r2,
+        1 if talk is not None else 0, _stream()),
         "attention")
+    if talk is not None:
+        _check(_fn("attention", "zk_attn_merge_talk")(_ptr(part_o), _ptr(part_ml), _ptr(talk), _ptr(out), n, n_heads, n_kv, vd,
+                                                      num_splits, dtype_code(q.dtype), _stream()), "attention merge (mixed heads)")
+        return out
     if num_splits > 1:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,
                                                  num_splits, dtype_code(q.dtype), _stream()), "attention merge")

@@ -9,6 +9,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache.manager import CallCacheSpec
 from ..config.base import ModelConfig
 from ..parts.base import Block, Norm, Part, WeightSpec, walk_parts
@@ -28,10 +29,14 @@ class LayerCall:
 class Model:
     def __init__(self, config: ModelConfig, embedding: TokenEmbedding, layers: Sequence[Block],
                  final_norm: Norm, head: LMHead, schedule: Optional[Sequence[LayerCall]] = None,
-                 ignorable_weights: Sequence[str] = (), depth_mix=None):
+                 ignorable_weights: Sequence[str] = (), depth_mix=None, pass_input=None):
         """depth_mix: a `parts.depth.DepthAverage` (or None): after every schedule entry the rows that go
-        on are a weighted sum of all results so far instead of the entry's result alone."""
+        on are a weighted sum of all results so far instead of the entry's result alone.
+        pass_input: a `parts.loop.PassInput` (or None): before the schedule entries it names, the rows are
+        given the embedding's rows again and a learned vector (repeated stretches of layers)."""
         self.config = config
+        self.pass_input = pass_input
+        self.tap = None         # debugging: called as tap(schedule index, rows) after every entry
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
         self.depth_mix = depth_mix
         self.schedule = list(schedule) if schedule is not None else [LayerCall(i) for i in range(len(self.layers))]
@@ -49,7 +54,7 @@ class Model:
         out: list[Part] = []
         seen: set[int] = set()
         tops = (self.embedding, *self.layers, self.final_norm, self.head)
-        for top in tops if self.depth_mix is None else (*tops, self.depth_mix):
+        for top in (*tops, *(p for p in (self.depth_mix, self.pass_input) if p is not None)):
             for p in walk_parts(top):
                 if id(p) not in seen:
                     seen.add(id(p))
@@ -93,10 +98,22 @@ class Model:
             x = mix.first_input(planes)
         else:
             x = self.embedding.forward(ctx, ctx.tokens)
+        passes, x_emb = self.pass_input, None
+        if passes is not None:
+            if mix is not None:
+                raise ValueError("a depth mix and pass inputs together are not supported")
+            if passes.needs_embedding:      # the embedding's rows are wanted again later: the layers work on a copy
+                x_emb = x
+                x = kernels.weighted_sum(x_emb.unsqueeze(0), None, 1, torch.empty_like(x_emb))
         carried = None      # what a block's last contraction prepared for the norm that reads x next
         for i, call_ctx in enumerate(calls):
+            if passes is not None and passes.starts_at(i):
+                passes.before(ctx, i, x, x_emb)
+                carried = None
             if mix is not None:
                 next_norm = None        # the rows the next norm reads are not the rows this block sums into
+            elif passes is not None and passes.starts_at(i + 1):
+                next_norm = None        # the rows change between this block and the next norm
             elif i + 1 < len(calls):
                 next_norm = self.layers[calls[i + 1].layer].entry_norm()
             else:
@@ -104,6 +121,8 @@ class Model:
             carried = self.layers[call_ctx.layer].forward_chained(ctx, call_ctx, x, carried, next_norm)
             if mix is not None:
                 x = mix.after(planes, i)
+            if self.tap is not None:
+                self.tap(i, x)
         if want_all:
             return self.head.forward(ctx, normed_for(self.head, self.final_norm, ctx, x, carried), out=out)
         if want_rows is None or want_rows.numel() == 0:

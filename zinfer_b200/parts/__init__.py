@@ -6,9 +6,12 @@ from .block import PreNormBlock, SublayerNormBlock
 from .depth import DepthAverage
 from .embedding import LMHead, TokenEmbedding
 from .feedforward import ActMlp, SwiGLU
+from .hgrn2 import Hgrn2
 from .linear import linear
+from .loop import PassInput
 from .moe import TableMoE
 from .norm import RMSNorm
 from .rope import RotaryEncoding
 from .seqconv import InputConv
+from .shift import TokenShift
 from .shortconv import ShortConv

@@ -15,7 +15,10 @@ Options that other designs use: `value_dim` (values of another width than keys),
 "all" (the q norm runs over all heads of a token at once with a weight of that width, likewise k;
 "head" is the per-head norm with a weight of head_dim), `distance_bias` = (name of r1, name of r2),
 two numbers per query head: r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query
-position i and key position j, in float32, before the softmax.
+position i and key position j, in float32, before the softmax.  `unit_norm_after_rotation`: q and k
+heads are divided by their root mean square (no weight, the layer's eps) after the position encoding.
+`talk_name`: a matrix T [heads, heads]; after the softmax head h's weights become
+sum_g T[h, g] * (weights of head g), and head h applies them to the values of its own key/value head.
 
 How the kernels are launched is decided here, not by the engine: the table of query tiles of a
 step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
@@ -87,7 +90,8 @@ class GqaAttention(Mixer):
                  v_name: str, out_name: str, q_norm_name: Optional[str] = None, k_norm_name: Optional[str] = None,
                  norm_eps: float = 1e-5, position: Optional[PositionEncoding] = None, window: int = 0,
                  scale: Optional[float] = None, split_keys: int = 0, value_dim: Optional[int] = None,
-                 qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True):
+                 qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True,
+                 unit_norm_after_rotation: bool = False, talk_name: Optional[str] = None):
         """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
         step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
@@ -97,12 +101,15 @@ class GqaAttention(Mixer):
         self.value_dim = head_dim if value_dim is None else int(value_dim)
         self.qk_norm_span, self.distance_bias, self.own_kv = qk_norm_span, distance_bias, bool(own_kv)
         # the kernel that prepares q and k over the whole projection has no rotation
-        self.span_prepare = qk_norm_span == "all" or self.value_dim != head_dim or not own_kv
-        if self.span_prepare and position is not None:
-            raise ValueError("attention: a position encoding goes with per-head norms, equal key and value widths "
-                             "and key/value weights of the mixer's own")
+        self.span_prepare = qk_norm_span == "all" or not own_kv
+        if self.span_prepare and (position is not None or unit_norm_after_rotation):
+            raise ValueError("attention: a position encoding and a norm behind it go with per-head norms and key/value "
+                             "weights of the mixer's own")
         if self.span_prepare and qk_norm_span == "head" and (q_norm_name or k_norm_name):
-            raise ValueError("attention: per-head norms go with equal key and value widths and own key/value weights")
+            raise ValueError("attention: per-head norms go with key/value weights of the mixer's own")
+        if talk_name is not None and distance_bias is not None:
+            raise ValueError("attention: no kernel takes a distance bias together with weights mixed across heads")
+        self.unit_norm_after, self.talk_name, self.talk = bool(unit_norm_after_rotation), talk_name, None
         self.bias_r1 = self.bias_r2 = None
         self.split_keys = int(split_keys)
         self._sm_count = 0
@@ -145,6 +152,8 @@ class GqaAttention(Mixer):
             specs.append(WeightSpec(self.k_norm_name, (self.kv_dim if whole else self.head_dim,), role="vector", init="norm"))
         if self.distance_bias is not None:
             specs += [WeightSpec(n, (self.n_heads,), role="vector", init="abs_normal") for n in self.distance_bias]
+        if self.talk_name is not None:
+            specs.append(WeightSpec(self.talk_name, (self.n_heads, self.n_heads), role="vector"))
         return specs
 
     def load(self, weights, dtype, device):
@@ -157,6 +166,7 @@ class GqaAttention(Mixer):
         self.k_norm = weights[self.k_norm_name] if self.k_norm_name and self.own_kv else None
         if self.distance_bias is not None:
             self.bias_r1, self.bias_r2 = (weights[n] for n in self.distance_bias)
+        self.talk = weights[self.talk_name] if self.talk_name is not None else None
         self._sm_count = kernels.sm_count(device) if torch.device(device).type == "cuda" else 0
 
     def kv_request(self):
@@ -165,10 +175,9 @@ class GqaAttention(Mixer):
 
     def check(self, dtype, page_size):
         most = kernels.attn_max_head_dim()
-        if self.span_prepare:
-            if not 0 < self.head_dim <= most or not 0 < self.value_dim <= most:
-                raise ValueError(f"attention: head_dim {self.head_dim} and value_dim {self.value_dim} must be at most {most}")
-        elif self.head_dim % 2 or self.head_dim > most:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
+        if not 0 < self.head_dim <= most or not 0 < self.value_dim <= most:
+            raise ValueError(f"attention: head_dim {self.head_dim} and value_dim {self.value_dim} must be at most {most}")
+        if not self.span_prepare and self.head_dim % 2:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
             raise ValueError(f"attention: head_dim {self.head_dim} must be even and at most {most}")
         if self.split_keys < 0 or self.split_keys % CHUNK_ALIGN:
             raise ValueError(f"attention: split_keys {self.split_keys} must be a multiple of {CHUNK_ALIGN}")
@@ -196,18 +205,21 @@ class GqaAttention(Mixer):
         elif fused:
             q = kernels.qk_prepare(qkv, kv.k, kv.v, self.q_norm, self.k_norm, rot.inv_freq if rot else None,
                                    n_rot=rot.n_rot if rot else 0, interleaved=rot.interleaved if rot else False,
-                                   write_kv=call.writes_kv, **common)
+                                   write_kv=call.writes_kv, value_dim=self.value_dim,
+                                   unit_norm_after=self.unit_norm_after, **common)
         else:
             # A position encoding that is not a rotation table runs between the norm and the
             # cache write: norm in place of a copy of qkv, the encoding's own step, then the write.
+            if self.value_dim != self.head_dim:
+                raise ValueError("attention: a position encoding of its own needs values as wide as the keys")
             normed = kernels.qk_normed(qkv, self.q_norm, self.k_norm, self.n_heads, self.n_kv, self.head_dim, self.eps,
                                        ctx.tok_pos, ctx.status)
             self.position.apply(ctx, normed[:, :self.q_dim], normed[:, self.q_dim:self.q_dim + self.kv_dim])
             q = kernels.qk_prepare(normed, kv.k, kv.v, None, None, None, n_rot=0, interleaved=False,
-                                   write_kv=call.writes_kv, **common)
+                                   write_kv=call.writes_kv, unit_norm_after=self.unit_norm_after, **common)
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
                                                    ctx.is_decode, self.window, self.value_dim,
-                                                   self.distance_bias is not None)
+                                                   self.distance_bias is not None, self.talk_name is not None)
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))
@@ -215,7 +227,8 @@ class GqaAttention(Mixer):
                                 kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
                                 num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
                                 value_dim=self.value_dim,
-                                bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None)
+                                bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None,
+                                talk=self.talk)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 

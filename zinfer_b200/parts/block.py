@@ -10,18 +10,40 @@ A part that sets `sums_through_linear = True` uses `out` only as the `out=` of i
 call.  It may then be handed, in place of the residual rows, what the NEXT norm's `ahead`
 returned (a `ResidualSink`), so that the kernel of that contraction writes the next norm's inputs
 beside the sum.  The next norm is the block's own second norm for the mixer, and for the
-feed-forward whatever the model says runs next (`forward_chained`)."""
+feed-forward whatever the model says runs next (`forward_chained`).
+
+Two options other designs use: no feed-forward at all (`ffn` and `ffn_norm` None: the block is its first
+sum alone), and layer scale: a sublayer's result is multiplied by a learned vector (`mixer_scale_name`,
+`ffn_scale_name`, one number per channel) before it is summed, x += s * Mixer(norm(x)).  A scaled sublayer
+writes into a float32 buffer and `kernels.scale_add` sums it in, so nothing is prepared for the next norm."""
 from __future__ import annotations
 
-from .base import BLOCKS, Block, FeedForward, Mixer, Norm
+from .base import BLOCKS, Block, FeedForward, Mixer, Norm, WeightSpec
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm | None = None, ffn: FeedForward | None = None,
+                 mixer_scale_name: str | None = None, ffn_scale_name: str | None = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        if ffn is None and ffn_scale_name is not None:
+            raise ValueError("a scale for a feed-forward that is not there")
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.mixer_scale_name, self.ffn_scale_name = mixer_scale_name, ffn_scale_name
+        self.mixer_scale = self.ffn_scale = None
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def weight_specs(self):
+        names = [n for n in (self.mixer_scale_name, self.ffn_scale_name) if n is not None]
+        if names and not hasattr(self.mixer_norm, "dim"):
+            raise ValueError(f"layer scale: {type(self.mixer_norm).__name__} does not tell the width of the rows (`dim`)")
+        return [WeightSpec(n, (self.mixer_norm.dim,), role="vector", init="norm") for n in names]
+
+    def load(self, weights, dtype, device):
+        self.mixer_scale = weights[self.mixer_scale_name] if self.mixer_scale_name is not None else None
+        self.ffn_scale = weights[self.ffn_scale_name] if self.ffn_scale_name is not None else None
 
     def entry_norm(self):
         return self.mixer_norm
@@ -30,9 +52,24 @@ class PreNormBlock(Block):
         self.forward_chained(ctx, call, x)
 
     def forward_chained(self, ctx, call, x, entry=None, next_norm=None):
-        mid = ahead_for(self.mixer, self.ffn_norm, ctx, x)
-        self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry),
-                           x if mid is None else mid, True)
+        from .. import kernels
+        import torch
+        mid = None
+        if self.mixer_scale is not None:
+            m = torch.empty_like(x)
+            self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry), m, False)
+            kernels.scale_add(m, self.mixer_scale, x)
+        else:
+            mid = ahead_for(self.mixer, self.ffn_norm if self.ffn_scale is None else None, ctx, x)
+            self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry),
+                               x if mid is None else mid, True)
+        if self.ffn is None:
+            return None
+        if self.ffn_scale is not None:
+            m = torch.empty_like(x)
+            self.ffn.forward(ctx, normed_for(self.ffn, self.ffn_norm, ctx, x, mid), m, False)
+            kernels.scale_add(m, self.ffn_scale, x)
+            return None
         last = ahead_for(self.ffn, next_norm, ctx, x)
         self.ffn.forward(ctx, normed_for(self.ffn, self.ffn_norm, ctx, x, mid), x if last is None else last, True)
         return last

@@ -3,7 +3,7 @@ into a model.  Each tensor's values depend only on (seed, tensor name), not on t
 generation, so a folder and an in-memory model of the same seed agree.
 
 Matrices and biases are N(0, std); norm weights are 1 + N(0, std) ("one_plus_normal") or
-N(0, std) ("normal").  Values are rounded to the storage dtype before use, so every reader of
+N(0, std) ("normal"); "unit_interval" tensors (bounds of gates, mixing weights) lie in (0, 1).  Values are rounded to the storage dtype before use, so every reader of
 the folder sees the same numbers.
 """
 from __future__ import annotations
@@ -33,6 +33,8 @@ def _tensor(spec: WeightSpec, seed: int, std: float, norm_init: str, storage_dty
         init = norm_init
     if init == "zeros":
         vals = np.zeros(count, dtype=np.float32)
+    elif init == "unit_interval":          # gates' bounds and mixing weights: anywhere in (0, 1), whatever `std`
+        vals = rng.random(count, dtype=np.float32) * np.float32(0.9) + np.float32(0.05)
     else:
         vals = rng.standard_normal(count, dtype=np.float32) * np.float32(std)
         if init == "one_plus_normal":
@@ -81,6 +83,9 @@ def random_tensors_on_device(model, seed: int, std: float, norm_init: str, stora
         t = torch.empty(spec.alt_shapes[0] if spec.alt_shapes else spec.shape, dtype=storage_dtype, device=device)
         if init == "zeros":
             t.zero_()
+        elif init == "unit_interval":
+            kernels.fill_normal(t, (seed << 32) ^ zlib.crc32(name.encode()), 0.0, 1.0)
+            t.copy_(torch.sigmoid(t.float()))
         elif init in ("normal", "one_plus_normal", "abs_normal"):
             kernels.fill_normal(t, (seed << 32) ^ zlib.crc32(name.encode()), 1.0 if init == "one_plus_normal" else 0.0, std)
             if init == "abs_normal":
