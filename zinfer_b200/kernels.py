@@ -892,8 +892,9 @@ def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_
     _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, None, head_dim))
     _need(v_cache, "v_cache", qkv.dtype, (None, n_kv, None, vd))
     page_size = k_cache.shape[2]
-    if head_dim % 2 or head_dim > attn_max_head_dim():
-        raise KernelError(f"qk_prepare: head_dim {head_dim} must be even and <= {attn_max_head_dim()}")
+    if head_dim > attn_max_head_dim() or vd > attn_max_head_dim() or n_rot % 2 or n_rot > head_dim:
+        raise KernelError(f"qk_prepare: head_dim {head_dim} and value_dim {vd} must be <= {attn_max_head_dim()}, "
+                          f"the rotated width {n_rot} even and <= head_dim")
     for wt, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
         if wt is not None:
             _need(wt, nm, torch.float32, (head_dim,))

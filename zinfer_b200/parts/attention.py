@@ -177,8 +177,6 @@ class GqaAttention(Mixer):
         most = kernels.attn_max_head_dim()
         if not 0 < self.head_dim <= most or not 0 < self.value_dim <= most:
             raise ValueError(f"attention: head_dim {self.head_dim} and value_dim {self.value_dim} must be at most {most}")
-        if not self.span_prepare and self.head_dim % 2:        # the reference: a multiple of 8, at most 512 (src/model.zig:1469)
-            raise ValueError(f"attention: head_dim {self.head_dim} must be even and at most {most}")
         if self.split_keys < 0 or self.split_keys % CHUNK_ALIGN:
             raise ValueError(f"attention: split_keys {self.split_keys} must be a multiple of {CHUNK_ALIGN}")
 
