@@ -80,6 +80,8 @@ class ZosuraxConfig(ModelConfig):
             if not isinstance(L, dict):
                 raise ConfigError(f"config.json: 'layers[{i}]' must be an object")
             kind = str(need(L, "type"))
+            if kind not in MIXER_TYPES:
+                raise ConfigError(f"config.json: '{w}type' = {kind!r}; known types are {list(MIXER_TYPES)}")
             m = _obj(L, "mixer", w)
             dim = as_int(m, w + "mixer.dim", need(m, "dim"), 1)
             heads = as_int(m, w + "mixer.heads", need(m, "heads"), 1)
