@@ -263,25 +263,63 @@ def lfm2_like(sz: dict) -> dict:
                 sliding_window=sz["window"], block_ff_dim=sz["top"] * sz["ff"] + sz["shared"], block_auto_adjust_ff_dim=False)
 
 
+# Zosurax beside the closest existing architecture at equal size: width, layers, vocabulary and the attention
+# layers' heads are the same; LFM2 has a short convolution where Zosurax has its HGRN2 recurrence, plain
+# grouped-query attention where Zosurax has either of its attention kinds, and a SwiGLU of two thirds the
+# hidden units (three matrices) where Zosurax has its squared-relu feed-forward of two: the same parameters.
+ZOSURAX_SIZES = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv=4, dim=64, rec_heads=8, rec_dim=128, ff=4096, vocab=32768),
+    "w2048": dict(width=2048, layers=8, heads=32, kv=8, dim=64, rec_heads=16, rec_dim=128, ff=8192, vocab=65536),
+}
+ZOSURAX_KINDS = ["hgrn2", "attention", "attention_2", "hgrn2", "attention", "attention_2", "hgrn2", "attention"]
+
+
+def zosurax_config(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        kind = ZOSURAX_KINDS[i % len(ZOSURAX_KINDS)]
+        if kind == "hgrn2":
+            mixer = {"heads": sz["rec_heads"], "dim": sz["rec_dim"], "vdim": sz["width"] // sz["rec_heads"]}
+        else:
+            mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["dim"] if kind == "attention" else sz["dim"] // 2}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": sz["ff"]}})
+    return {"architecture": "Zosurax", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def lfm2_like_zosurax(sz: dict) -> dict:
+    kinds = ["conv" if ZOSURAX_KINDS[i % len(ZOSURAX_KINDS)] == "hgrn2" else "full_attention" for i in range(sz["layers"])]
+    return dict(LFM2_1_2B, vocab_size=sz["vocab"], hidden_size=sz["width"], num_hidden_layers=sz["layers"],
+                num_attention_heads=sz["heads"], num_key_value_heads=sz["kv"], head_dim=sz["dim"],
+                max_position_embeddings=CONTEXT, layer_types=kinds, block_ff_dim=-(-(sz["ff"] * 2 // 3) // 256) * 256,
+                block_auto_adjust_ff_dim=False)
+
+
+COMPARISONS = {"ponusun": (PONUSUN_SIZES, ponusun_config, lfm2_like), "zosurax": (ZOSURAX_SIZES, zosurax_config, lfm2_like_zosurax)}
+
+
 def ponusun_arm(args) -> dict:
-    """Prompt and single-token throughput of Ponusun and of LFM2 at equal size, random weights, bfloat16:
-    one prompt of --prefill-tokens tokens in one step (median of 5), then --steps single-token steps of
-    --batch sequences replayed from CUDA graphs (prompts of 512..2,048 tokens)."""
+    """Prompt and single-token throughput of Ponusun (or Zosurax, `--model zosurax`) and of LFM2 at equal size, random
+    weights, bfloat16: one prompt of --prefill-tokens tokens in one step (median of 5), then --steps single-token
+    steps of --batch sequences replayed from CUDA graphs (prompts of 512..2,048 tokens)."""
     import numpy as np
     import torch
     import zinfer_b200 as z
     from zinfer_b200 import kernels
 
     kernels.require_cuda()
-    out = {"metric": "prompt and single-token tokens/s, Ponusun beside LFM2 at equal size (random weights)", "unit": "tokens/s",
+    new = args.model
+    sizes, new_config, like_config = COMPARISONS[new]
+    out = {"metric": f"prompt and single-token tokens/s, {new.capitalize()} beside LFM2 at equal size (random weights)", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup, "batch": args.batch,
            "prefill_tokens": args.prefill_tokens, "sizes": {}}
-    wanted = [args.size] if args.size else list(PONUSUN_SIZES)
+    wanted = [args.size] if args.size else list(sizes)
     with ClockSampler() as clocks:
         for name in wanted:
-            sz = PONUSUN_SIZES[name]
+            sz = sizes[name]
             row = {}
-            for arch, cfg_dict in (("ponusun", ponusun_config(sz)), ("lfm2", lfm2_like(sz))):
+            for arch, cfg_dict in ((new, new_config(sz)), ("lfm2", like_config(sz))):
                 if args.arch and arch != args.arch:
                     continue
                 cfg = z.config_from_dict(cfg_dict)
@@ -314,9 +352,9 @@ def ponusun_arm(args) -> dict:
                 row[arch] = res
                 del engine, model
                 torch.cuda.empty_cache()
-            if "ponusun" in row and "lfm2" in row:
-                row["ponusun_over_lfm2"] = {k: round(row["ponusun"][k]["tokens_per_s"] / row["lfm2"][k]["tokens_per_s"], 3)
-                                            for k in row["ponusun"]}
+            if new in row and "lfm2" in row:
+                row[f"{new}_over_lfm2"] = {k: round(row[new][k]["tokens_per_s"] / row["lfm2"][k]["tokens_per_s"], 3)
+                                           for k in row[new]}
             out["sizes"][name] = dict(row, config={k: sz[k] for k in sz})
     out["clocks"] = clocks.summary()
     return out
@@ -423,11 +461,12 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: the prompt's length (the headline line always uses 2,048)")
-    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun"] + sorted(SECONDARY),
-                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun: the "
-                         "Ponusun architecture beside LFM2 at equal size, prompt and single-token steps")
-    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun: one size only")
-    ap.add_argument("--arch", default="", choices=["", "ponusun", "lfm2"], help="with --model ponusun: one architecture only")
+    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun", "zosurax"] + sorted(SECONDARY),
+                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun, zosurax: "
+                         "that architecture beside LFM2 at equal size, prompt and single-token steps")
+    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun or zosurax: one size only")
+    ap.add_argument("--arch", default="", choices=["", "ponusun", "zosurax", "lfm2"],
+                    help="with --model ponusun or zosurax: one architecture only")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
@@ -438,7 +477,7 @@ def main() -> int:
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: zinfer_b200 runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.model == "ponusun":
+    if args.model in COMPARISONS:
         print(json.dumps(ponusun_arm(args)))
         return 0
     print(json.dumps(own_arm(args) if args.model == "1.2b" else secondary_arm(args)))

@@ -72,7 +72,10 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
                           const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                           const int* __restrict__ page_table, int pt_stride, int n_seqs, int H, int Hkv, int page_size,
                           int window, float scale, int num_splits, int split_keys, const float* __restrict__ bias_r1,
-                          const float* __restrict__ bias_r2) {
+                          const float* __restrict__ bias_r2, int cross) {
+  // cross: blockIdx.y also counts the key/value heads whose VALUES a block reads in place of its own
+  // key/value head's, and the unnormalised sums always go to part_o / part_ml, rows ordered
+  // (split, sequence, head, value head): for a kernel that mixes the heads' weights after the softmax.
   // bias_r1, bias_r2 [H] (both or neither): r1_h * ln(1 + r2_h * distance) is taken off the scaled score of the
   // key `distance` tokens behind the query, in float32 (here on base 2, like the scores).
   constexpr int KS = HD / 16;               // k steps of Q K^T
@@ -86,7 +89,11 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int G = H / Hkv;
-  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int b = blockIdx.x, kvh = blockIdx.y % Hkv, split = blockIdx.z;
+  const int vh = cross ? blockIdx.y / Hkv : kvh;
+  // the value rows read with a key/value head's keys: its own, or (cross) those of head vh, which lie
+  // (vh - kvh) * page_size rows further on in the same page
+  const bf16* v_rows = v_cache + (ptrdiff_t)(vh - kvh) * page_size * HD;
   const int L = seq_start[b] + 1;  // keys 0 .. L-1; the new token's own key is the last
   const int lo = (window > 0 && L > window) ? L - window : 0;
   int c0 = lo, c1 = L;             // this block's keys [c0, c1)
@@ -134,7 +141,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     }
     if (page >= 0 && kb + DT_TK <= c1) {     // a whole tile: nothing to test per piece
       const bf16* kg = k_cache + base + g_off0;
-      const bf16* vg = v_cache + base + g_off0;
+      const bf16* vg = v_rows + base + g_off0;
       unsigned char* ks = Ksm(buf) + sm_off0;
       unsigned char* vs = Vsm(buf) + sm_off0;
 #pragma unroll
@@ -148,7 +155,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
         const bool valid = page >= 0 && kb + r < c1;
         const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
         cp_async16(Ksm(buf) + swz<HD>(r, ch), k_cache + off, valid);
-        cp_async16(Vsm(buf) + swz<HD>(r, ch), v_cache + off, valid);
+        cp_async16(Vsm(buf) + swz<HD>(r, ch), v_rows + off, valid);
       }
     }
     cp_async_commit();
@@ -308,10 +315,10 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       O = fmaf(e, sm_o[(w * 16 + h) * HD + d], O);
     }
     const int head = kvh * G + h;
-    if (num_splits == 1) {
+    if (num_splits == 1 && !cross) {
       out[(size_t)b * H * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
     } else {
-      const size_t row = ((size_t)split * n_seqs + b) * H + head;
+      const size_t row = cross ? (((size_t)split * n_seqs + b) * H + head) * Hkv + vh : ((size_t)split * n_seqs + b) * H + head;
       part_o[row * HD + d] = O;
       if (d == 0) {
         part_ml[row * 2] = M;
@@ -325,7 +332,7 @@ template <int HD, int NST>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int Hkv,
            int page_size, int window, float scale, int num_splits, int split_keys, const float* r1, const float* r2,
-           cudaStream_t stream) {
+           int cross, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<HD, NST>;
   const size_t smem = 2 * NST * (size_t)DT_TK * HD * 2;
   static_assert(2 * NST * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
@@ -333,10 +340,10 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(n_seqs, Hkv, num_splits);
+  dim3 grid(n_seqs, Hkv * (cross ? Hkv : 1), num_splits);
   return zk_launch_dependent(kern, grid, dim3(DT_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, Hkv,
-                                              page_size, window, scale, num_splits, split_keys, r1, r2);
+                                              page_size, window, scale, num_splits, split_keys, r1, r2, cross);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -357,8 +364,9 @@ int zk_attn_decode_tc_takes(int H, int Hkv, int hd, int page_size) {
 int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                       const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H,
                       int Hkv, int hd, int page_size, int window, float scale, int num_splits, int split_keys,
-                      const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
+                      const float* bias_r1, const float* bias_r2, int cross, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  if (cross && (!part_o || !part_ml)) return ZK_EINVAL;
   if (!zk_attn_decode_tc_takes(H, Hkv, hd, page_size) || num_splits < 1) return ZK_EINVAL;
   if ((bias_r1 == nullptr) != (bias_r2 == nullptr)) return ZK_EINVAL;
   if (num_splits > 1 && (split_keys <= 0 || split_keys % DT_TK || !part_o || !part_ml)) return ZK_EINVAL;
@@ -371,12 +379,12 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
   if (hd == 64 && short_chunks)
     return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
   if (hd == 64)
     return launch<64, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
   return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, stream);
+                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
 }
 
 }  // extern "C"

@@ -61,9 +61,13 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
                         const int* __restrict__ cu_q, const int* __restrict__ seq_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
                         int Hkv, int page_size, int window, float scale, const float* __restrict__ bias_r1,
-                        const float* __restrict__ bias_r2) {
+                        const float* __restrict__ bias_r2, float* __restrict__ part_o, float* __restrict__ part_ml) {
   // bias_r1, bias_r2 [H] (both or neither): r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of
   // query position i and key position j, in float32, before the softmax.
+  // part_o, part_ml (both or neither): the cross mode.  blockIdx.z names a key/value head whose VALUES this
+  // block reads in place of its own key/value head's, and the unnormalised sums with their maximum and
+  // denominator go to part_o [tokens * H * Hkv, HD] and part_ml [tokens * H * Hkv, 2], rows ordered
+  // (token, head, value head), for a kernel that mixes the heads' weights after the softmax.
   constexpr int BQ = PF_ROWS / GP;          // tokens per block
   constexpr int KS = HD / 16;               // k steps of Q K^T
   constexpr int CH = HD / 8;                // 16-byte chunks per row
@@ -76,6 +80,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
   const int g = lane >> 2, c = lane & 3;
   const int G = H / Hkv, chunks = G / GP;
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const bool cross = part_o != nullptr;
+  const int vh = cross ? blockIdx.z : kvh;
   // tiles are taken from the last (a sequence's late tokens see the most keys) to the first, so
   // that the long blocks start first and the short ones fill the tail
   const int tile = gridDim.x - 1 - blockIdx.x;
@@ -132,12 +138,13 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
     const int kb = k_begin + t * PF_TK;
     const int page = pt[kb / page_size];
     const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + kb % page_size) * HD;
+    const size_t vbase = (((size_t)(page < 0 ? 0 : page) * Hkv + vh) * page_size + kb % page_size) * HD;
     for (int i = tid; i < PF_TK * CH; i += PF_WARPS * 32) {
       const int r = i / CH, ch = i % CH;
       const bool valid = page >= 0 && kb + r < k_end;
-      const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
-      cp_async16(Ksm[buf] + swz<HD>(r, ch), k_cache + off, valid);
-      cp_async16(Vsm[buf] + swz<HD>(r, ch), v_cache + off, valid);
+      const size_t off = (size_t)(valid ? r : 0) * HD + ch * 8;
+      cp_async16(Ksm[buf] + swz<HD>(r, ch), k_cache + base + off, valid);
+      cp_async16(Vsm[buf] + swz<HD>(r, ch), v_cache + vbase + off, valid);
     }
     cp_async_commit();
   };
@@ -248,6 +255,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!row_ok[h]) continue;
+    if (cross) {
+      const size_t row = ((size_t)row_tok[h] * H + row_head[h]) * Hkv + vh;
+      float* dst = part_o + row * HD;
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j)
+        *reinterpret_cast<float2*>(dst + 8 * j + 2 * c) = make_float2(o[j][2 * h], o[j][2 * h + 1]);
+      if (c == 0) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m_run[h], l_run[h]);
+      continue;
+    }
     const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
     bf16* dst = out + (size_t)row_tok[h] * H * HD + (size_t)row_head[h] * HD;
 #pragma unroll
@@ -259,18 +275,18 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
 template <int HD, int GP>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_q0,
            const int* cu_q, const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_tiles,
-           int H, int Hkv, int page_size, int window, float scale, const float* r1, const float* r2,
-           cudaStream_t stream) {
+           int H, int Hkv, int page_size, int window, float scale, const float* r1, const float* r2, float* part_o,
+           float* part_ml, cudaStream_t stream) {
   auto kern = attn_prefill_kernel<HD, GP>;
   const size_t smem = 4 * (size_t)PF_TK * HD * 2;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(n_tiles, Hkv * ((H / Hkv) / GP));
+  dim3 grid(n_tiles, Hkv * ((H / Hkv) / GP), part_o ? Hkv : 1);
   kern<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, pt_stride, H,
-                                              Hkv, page_size, window, scale, r1, r2);
+                                              Hkv, page_size, window, scale, r1, r2, part_o, part_ml);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -292,18 +308,22 @@ int zk_attn_prefill_takes(int H, int Hkv, int hd, int page_size) {
 }
 int zk_attn_prefill_tile_tokens(int H, int Hkv) { return PF_ROWS / packed_heads(H / Hkv); }
 
-// q, out [n_tokens, H*hd] bfloat16; tiles of zk_attn_prefill_tile_tokens tokens.
+// q, out [n_tokens, H*hd] bfloat16; tiles of zk_attn_prefill_tile_tokens tokens.  part_o [n_tokens*H*Hkv, hd] and
+// part_ml [n_tokens*H*Hkv, 2] float32 (both or neither) switch the cross mode on: `out` is then not written.
 int zk_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                     const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                     const int* page_table, int pt_stride, int n_tiles, int H, int Hkv, int hd, int page_size,
-                    int window, float scale, const float* bias_r1, const float* bias_r2, cudaStream_t stream) {
+                    int window, float scale, const float* bias_r1, const float* bias_r2, float* part_o, float* part_ml,
+                    cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!zk_attn_prefill_takes(H, Hkv, hd, page_size) || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
+  if ((part_o == nullptr) != (part_ml == nullptr) || (part_o && Hkv > 65535)) return ZK_EINVAL;
   const int gp = packed_heads(H / Hkv);
 #define ZK_PF(HDV, GPV)                                                                                          \
   if (hd == HDV && gp == GPV)                                                                                    \
     return launch<HDV, GPV>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,  \
-                            pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, stream);
+                            pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, part_o, part_ml,  \
+                            stream);
   ZK_PF(64, 1) ZK_PF(64, 2) ZK_PF(64, 4) ZK_PF(64, 8)
   ZK_PF(128, 1) ZK_PF(128, 2) ZK_PF(128, 4) ZK_PF(128, 8)
 #undef ZK_PF

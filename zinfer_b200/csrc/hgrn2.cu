@@ -7,87 +7,137 @@
 // [q (H*d) | f (H*d) | v (H*e)], float32 as the contraction left them; the gate is
 // f = lower + (1 - lower) * sigmoid(z_f + bias).  Everything here is float32: gate, state, sums.
 //
-// One kernel serves prompt steps and single-token steps.  A block owns one (sequence, head, stretch of
-// value columns); a thread owns one column of S (d values in registers) and walks the sequence's
-// tokens in order, from the state the step before left in `state[slot]` to the state it leaves there.
-// q, f and 1 - f of eight tokens at a time are staged in shared memory (activations applied once per
-// block), every thread reads them as broadcasts.  The sum over a column runs over the channels in
-// ascending order whatever the step's shape, so a sequence cut into steps gives the same bits.
+// One kernel serves prompt steps and single-token steps.  A block owns one (sequence, head, 32 value columns)
+// and walks the sequence's tokens in order, from the state the step before left in `state[slot]` to the
+// state it leaves there.  Its eight warps split the d channels: warp w keeps rows [w*DPT, (w+1)*DPT) of the
+// 32 columns of S in registers (lane = column, so the state is read and written in whole lines), adds up its
+// part of o_t = sum_i S_t[i, c] q_t[i], and the parts of eight tokens at a time meet in shared memory, where
+// warp w sums those of token w in the order of the warps.  q and f of the next eight tokens are fetched into
+// registers while the current eight are worked on, and are turned into silu(q) and the gate on their way
+// into the other half of a double buffer.  The order of every sum is fixed by the layout alone, so a
+// sequence cut into steps gives the same bits as the whole.
 #include "common.cuh"
 #include <math.h>
 
-#define HG_TT 8            // tokens staged at once
+#define HG_TT 8            // tokens staged at once; also the warps of a block
+#define HG_R 8             // warps of a block, each with a stretch of the d channels
 #define HG_MAX_D 256
-#define HG_MAX_COLS 128    // value columns (threads) per block
 
-template <int DMAX>
-__global__ void __launch_bounds__(HG_MAX_COLS)
+template <int DPT>
+__global__ void __launch_bounds__(HG_R * 32)
     hgrn2_scan_kernel(const float* __restrict__ qfv, int ld, const float* __restrict__ f_bias,
                       const float* __restrict__ lower, float* __restrict__ state, long long state_stride,
                       float* __restrict__ o, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int H, int d,
                       int e) {
-  __shared__ __align__(16) float qs[HG_TT][DMAX];
-  __shared__ __align__(16) float fs[HG_TT][DMAX];
-  __shared__ __align__(16) float gs[HG_TT][DMAX];
+  constexpr int DM = HG_R * DPT;                                     // channels the block covers, >= d
+  constexpr int NL = (HG_TT * DM + HG_R * 32 - 1) / (HG_R * 32);     // q (and f) values a thread fetches per eight tokens
+  __shared__ __align__(16) float qs[2][HG_TT][DM];
+  __shared__ __align__(16) float fs[2][HG_TT][DM];
+  __shared__ float part[HG_TT][HG_R][32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x, h = blockIdx.y;
-  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int c = blockIdx.z * 32 + lane;
   const bool col = c < e;
+  const int row0 = warp * DPT;
+  // channels beyond d: q = 0 and f = 0 for good, so they add nothing
+  for (int i = tid; i < 2 * HG_TT * DM; i += HG_R * 32) {
+    (&qs[0][0][0])[i] = 0.f;
+    (&fs[0][0][0])[i] = 0.f;
+  }
+  __syncthreads();
   zk_let_next_start();
   zk_wait_prior();   // qfv is the kernel before's result
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
   float* st = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
-  float S[DMAX];
+  float S[DPT];
 #pragma unroll
-  for (int i = 0; i < DMAX; ++i) S[i] = (col && i < d) ? st[(size_t)i * e + c] : 0.f;
+  for (int k = 0; k < DPT; ++k) S[k] = (col && row0 + k < d) ? st[(size_t)(row0 + k) * e + c] : 0.f;
 
   const int off_f = H * d, off_v = 2 * H * d;
-  for (int tb = t0; tb < t1; tb += HG_TT) {
+  float rq[NL], rf[NL], v_cur[HG_TT], v_next[HG_TT];
+  auto fetch = [&](int tb) {
     const int nt = min(HG_TT, t1 - tb);
-    __syncthreads();   // the tokens staged before are consumed
-    for (int idx = threadIdx.x; idx < nt * d; idx += blockDim.x) {
+#pragma unroll
+    for (int n = 0; n < NL; ++n) {
+      const int idx = tid + n * HG_R * 32;
       const int tt = idx / d, i = idx - tt * d;
-      const float* row = qfv + (size_t)(tb + tt) * ld;
-      const float zq = row[h * d + i];
-      const float zf = row[off_f + h * d + i] + f_bias[h * d + i];
-      const float lo = lower[h * d + i];
-      const float f = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-zf)));
-      qs[tt][i] = zq / (1.0f + expf(-zq));
-      fs[tt][i] = f;
-      gs[tt][i] = 1.0f - f;
+      const bool ok = idx < nt * d;
+      const float* row = qfv + (size_t)(tb + (ok ? tt : 0)) * ld + h * d + (ok ? i : 0);
+      rq[n] = ok ? row[0] : 0.f;
+      rf[n] = ok ? row[off_f] : 0.f;
     }
-    float v[HG_TT];
 #pragma unroll
     for (int tt = 0; tt < HG_TT; ++tt)
-      v[tt] = (col && tt < nt) ? qfv[(size_t)(tb + tt) * ld + off_v + h * e + c] : 0.f;
-    __syncthreads();
+      v_next[tt] = (col && tt < nt) ? qfv[(size_t)(tb + tt) * ld + off_v + h * e + c] : 0.f;
+  };
+  auto stage = [&](int buf, int tb) {
+    const int nt = min(HG_TT, t1 - tb);
+#pragma unroll
+    for (int n = 0; n < NL; ++n) {
+      const int idx = tid + n * HG_R * 32;
+      if (idx < nt * d) {
+        const int tt = idx / d, i = idx - tt * d;
+        const float zq = rq[n], zf = rf[n] + f_bias[h * d + i], lo = lower[h * d + i];
+        qs[buf][tt][i] = zq / (1.0f + expf(-zq));
+        fs[buf][tt][i] = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-zf)));
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < HG_TT; ++tt) v_cur[tt] = v_next[tt];
+  };
+
+  if (t0 < t1) {
+    fetch(t0);
+    stage(0, t0);
+  }
+  __syncthreads();
+  int buf = 0;
+  for (int tb = t0; tb < t1; tb += HG_TT, buf ^= 1) {
+    const int nt = min(HG_TT, t1 - tb);
+    const bool more = tb + HG_TT < t1;
+    if (more) fetch(tb + HG_TT);       // under way while this group is worked on
 #pragma unroll
     for (int tt = 0; tt < HG_TT; ++tt) {
-      if (tt >= nt) break;
-      float acc = 0.f;
+      if (tt < nt) {
+        const float v = v_cur[tt];
+        float acc = 0.f;
+        if constexpr (DPT % 4 == 0) {
 #pragma unroll
-      for (int i4 = 0; i4 < DMAX; i4 += 4) {
-        if (i4 < d) {
-          const float4 f4 = *reinterpret_cast<const float4*>(&fs[tt][i4]);
-          const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][i4]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][i4]);
-          const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, gg[4] = {g4.x, g4.y, g4.z, g4.w},
-                      qq[4] = {q4.x, q4.y, q4.z, q4.w};
+          for (int k4 = 0; k4 < DPT; k4 += 4) {
+            const float4 f4 = *reinterpret_cast<const float4*>(&fs[buf][tt][row0 + k4]);
+            const float4 q4 = *reinterpret_cast<const float4*>(&qs[buf][tt][row0 + k4]);
+            const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (i4 + j < d) {
-              S[i4 + j] = fmaf(ff[j], S[i4 + j], gg[j] * v[tt]);
-              acc = fmaf(S[i4 + j], qq[j], acc);
+            for (int j = 0; j < 4; ++j) {
+              S[k4 + j] = fmaf(ff[j], S[k4 + j], fmaf(-ff[j], v, v));     // f S + (1 - f) v
+              acc = fmaf(S[k4 + j], qq[j], acc);
             }
           }
+        } else {
+#pragma unroll
+          for (int k = 0; k < DPT; ++k) {
+            const float f = fs[buf][tt][row0 + k];
+            S[k] = fmaf(f, S[k], fmaf(-f, v, v));
+            acc = fmaf(S[k], qs[buf][tt][row0 + k], acc);
+          }
         }
+        part[tt][warp][lane] = acc;
       }
-      if (col) o[(size_t)(tb + tt) * H * e + (size_t)h * e + c] = acc;
     }
+    __syncthreads();
+    if (warp < nt && col) {
+      float sum = 0.f;
+#pragma unroll
+      for (int r = 0; r < HG_R; ++r) sum += part[warp][r][lane];
+      o[(size_t)(tb + warp) * H * e + (size_t)h * e + c] = sum;
+    }
+    if (more) stage(buf ^ 1, tb + HG_TT);
+    __syncthreads();
   }
   if (col) {
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i)
-      if (i < d) st[(size_t)i * e + c] = S[i];
+    for (int k = 0; k < DPT; ++k)
+      if (row0 + k < d) st[(size_t)(row0 + k) * e + c] = S[k];
   }
 }
 
@@ -102,17 +152,17 @@ int zk_hgrn2_scan(const float* qfv, int ld, const float* f_bias, const float* lo
                   float* o, const int* cu_q, const int* seq_slot, int n_seqs, int H, int d, int e, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (H <= 0 || d <= 0 || e <= 0 || d > HG_MAX_D || ld < 2 * H * d + H * e || !f_bias || !lower) return ZK_EINVAL;
-  int threads = 32;
-  while (threads < HG_MAX_COLS && threads < e) threads <<= 1;
-  dim3 grid(n_seqs, H, (e + threads - 1) / threads);
-#define ZK_HG(DM)                                                                                                   \
-  return zk_launch_dependent(hgrn2_scan_kernel<DM>, grid, dim3(threads), 0, stream, qfv, ld, f_bias, lower, state,  \
+  dim3 grid(n_seqs, H, (e + 31) / 32);
+#define ZK_HG(DP)                                                                                                     \
+  return zk_launch_dependent(hgrn2_scan_kernel<DP>, grid, dim3(HG_R * 32), 0, stream, qfv, ld, f_bias, lower, state, \
                              state_stride, o, cu_q, seq_slot, H, d, e)
-  if (d <= 16) ZK_HG(16);
-  if (d <= 32) ZK_HG(32);
-  if (d <= 64) ZK_HG(64);
-  if (d <= 128) ZK_HG(128);
-  ZK_HG(256);
+  const int dpt = (d + HG_R - 1) / HG_R;
+  if (dpt <= 1) ZK_HG(1);
+  if (dpt <= 2) ZK_HG(2);
+  if (dpt <= 4) ZK_HG(4);
+  if (dpt <= 8) ZK_HG(8);
+  if (dpt <= 16) ZK_HG(16);
+  ZK_HG(32);
 #undef ZK_HG
 }
 

@@ -81,7 +81,7 @@ _SIGNATURES = {
         "zk_attn_decode_noalloc_bytes": "iiii",
     },
     "attention_prefill": {
-        "zk_attn_prefill": "pppppppppp" + "iiiiiiif" + "pp" + "p",
+        "zk_attn_prefill": "pppppppppp" + "iiiiiiif" + "pp" + "pp" + "p",
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
@@ -91,7 +91,7 @@ _SIGNATURES = {
         "zk_attn_prefill_tc5_tile_tokens": "ii",
     },
     "attention_decode_tc": {
-        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "p",
+        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "p",
         "zk_attn_decode_tc_takes": "iiii",
     },
     "sampling": {
@@ -985,15 +985,15 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
     taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
-    are mixed across the heads after the softmax (`talking`) by the general kernel."""
+    are mixed across the heads after the softmax (`talking`) by the same three."""
     same_width = value_dim is None or value_dim == head_dim
-    if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0 and not talking:
-        if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+    if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
+        if (not single_token and window <= 0 and not biased and not talking and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
-        if single_token and not biased and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
+        if single_token and not biased and not talking and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token", 1
         if not single_token and _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim, page_size):
             return "prompt_tc", _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_kv)
@@ -1013,8 +1013,8 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     row if it is not head_dim.  `bias` = (r1, r2), float32 [H] each: r1_h * ln(1 + r2_h * (i - j)) is taken
     off the scaled score of query position i and key position j.  Both are the general kernel's.
     `talk` float32 [H, H]: after the softmax head h's weights become sum_g talk[h, g] * (head g's weights), and
-    head h applies them to the values of its own key/value head (general kernel: every head's weights meet
-    every key/value head's values, and a merge kernel mixes the results)."""
+    head h applies them to the values of its own key/value head (general kernel and the two mma.sync kernels:
+    every head's weights meet every key/value head's values, and a merge kernel mixes the results)."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
     vd = head_dim if value_dim is None else int(value_dim)
@@ -1025,7 +1025,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             _need(b, nm, torch.float32, (n_heads,))
     if talk is not None:
         _need(talk, "talk", torch.float32, (n_heads, n_heads))
-        if kind not in (None, "general"):
+        if kind not in (None, "general", "prompt_tc", "single_token_tc"):
             raise KernelError(f"attention: the '{kind}' kernel mixes no weights across heads")
     if vd != head_dim and kind not in (None, "general"):
         raise KernelError(f"attention: the '{kind}' kernel takes no value width of its own")
@@ -1042,7 +1042,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     bq, gc = attn_tile_shape(n_heads, n_kv)
     n_tiles = tile_seq.numel()
     out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
-    if vd != head_dim or talk is not None or (bias is not None and kind != "single_token_tc"):
+    if vd != head_dim or (talk is not None and kind != "single_token_tc") or (bias is not None and kind != "single_token_tc"):
         single_token = False        # the general kernel runs single tokens as tiles of one query
     part_o = part_ml = None
     value_heads = n_kv if talk is not None else 1
@@ -1067,14 +1067,18 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention_prefill", "zk_attn_prefill")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
-            page_size, window, scale, r1, r2, _stream()), "attention (prompt, tensor cores)")
-        return out
+            page_size, window, scale, r1, r2, _ptr(part_o) if talk is not None else None,
+            _ptr(part_ml) if talk is not None else None, _stream()), "attention (prompt, tensor cores)")
+        return out if talk is None else _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, 1)
     if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
             and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
-            scale, num_splits, split_keys, r1, r2, _stream()), "attention (single token, tensor cores)")
+            scale, num_splits, split_keys, r1, r2, 1 if talk is not None else 0, _stream()),
+            "attention (single token, tensor cores)")
+        if talk is not None:
+            return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
         if num_splits > 1:
             _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
                                                      num_splits, dtype_code(q.dtype), _stream()), "attention merge")
@@ -1098,12 +1102,18 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         1 if talk is not None else 0, _stream()),
         "attention")
     if talk is not None:
-        _check(_fn("attention", "zk_attn_merge_talk")(_ptr(part_o), _ptr(part_ml), _ptr(talk), _ptr(out), n, n_heads, n_kv, vd,
-                                                      num_splits, dtype_code(q.dtype), _stream()), "attention merge (mixed heads)")
-        return out
+        return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
     if num_splits > 1:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,
                                                  num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+    return out
+
+
+def _merge_talk(part_o, part_ml, talk, out, n: int, n_heads: int, n_kv: int, vd: int, num_splits: int) -> torch.Tensor:
+    """out[t, h] = sum_g talk[h, g] * (head g's weights applied to the values of h's key/value head), from the
+    unnormalised sums the attention kernels' cross mode left per (split, token, head, value head)."""
+    _check(_fn("attention", "zk_attn_merge_talk")(_ptr(part_o), _ptr(part_ml), _ptr(talk), _ptr(out), n, n_heads, n_kv, vd,
+                                                  num_splits, dtype_code(out.dtype), _stream()), "attention merge (mixed heads)")
     return out
 
 
