@@ -66,6 +66,12 @@ struct Params {
   int* status;
   int pt_stride, H, Hkv, page_size, gp;   // gp: heads of a KV group packed into one block
   float scale;
+  // cross mode (both or neither): blockIdx.z names the key/value head whose VALUES a block reads in place of its
+  // own key/value head's, and the block's normalised rows go, as float32, to part_o [tokens * H * Hkv, HD] with
+  // (maximum 0, denominator 1) in part_ml [tokens * H * Hkv, 2], rows ordered (token, head, value head): what
+  // the kernel that mixes the heads' weights after the softmax reads.
+  float* part_o;
+  float* part_ml;
 };
 
 // 2^x on the special-function unit (relative error about 2^-22; 2^-inf = 0).
@@ -105,6 +111,8 @@ __global__ void __launch_bounds__(THREADS, 2)
   const int GP = p.gp, G = p.H / p.Hkv, chunks = G / GP;
   const int BQ = ROWS / GP;                   // tokens per block
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const bool cross = p.part_o != nullptr;
+  const int vh = cross ? blockIdx.z : kvh;
   // tiles are taken from the last (a sequence's late tokens see the most keys) to the first
   const int tile = gridDim.x - 1 - blockIdx.x;
   const int b = p.tile_seq[tile], q0 = p.tile_q0[tile];
@@ -162,7 +170,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int row = (page * p.Hkv + kvh) * p.page_size + kb % p.page_size;
       mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
       tma_load_2d(k_sm(s), &map_k, 0, row, &kv_full[s]);
-      tma_load_2d(v_sm(s), &map_v, 0, row, &kv_full[s]);
+      tma_load_2d(v_sm(s), &map_v, 0, row + (vh - kvh) * p.page_size, &kv_full[s]);
     }
   } else if (warp == 9 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
@@ -315,10 +323,21 @@ __global__ void __launch_bounds__(THREADS, 2)
       const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
       bf16* dst = p.out + (size_t)(t_base + min(q0 + tq, Tq - 1)) * p.H * HD + (size_t)(kvh * G + chunk * GP + hl) * HD +
                   half * HO;
+      const size_t xrow = ((size_t)(t_base + min(q0 + tq, Tq - 1)) * p.H + (kvh * G + chunk * GP + hl)) * p.Hkv + vh;
+      if (cross && row_ok && half == 0) *reinterpret_cast<float2*>(p.part_ml + xrow * 2) = make_float2(0.f, 1.f);
 #pragma unroll
       for (int c0 = 0; c0 < HO; c0 += 16) {
         float o[16];
         tmem_ld16(tmem_o + lane_sel + (unsigned)(half * HO + c0), o);
+        if (cross) {
+          if (row_ok) {
+            float* xdst = p.part_o + xrow * HD + half * HO + c0;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(xdst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+          }
+          continue;
+        }
         uint4 w0, w1;
         w0.x = pack_bf16(o[0] * inv, o[1] * inv);   w0.y = pack_bf16(o[2] * inv, o[3] * inv);
         w0.z = pack_bf16(o[4] * inv, o[5] * inv);   w0.w = pack_bf16(o[6] * inv, o[7] * inv);
@@ -372,12 +391,15 @@ int zk_attn_prefill_tc5_takes(int H, int Hkv, int hd, int page_size, int window)
 int zk_attn_prefill_tc5_tile_tokens(int H, int Hkv) { return ROWS / packed_heads(H / Hkv); }
 
 // q, out [n_tokens, H*64] bfloat16; k_cache, v_cache [num_pages, Hkv, page_size, 64] bfloat16;
-// tiles of zk_attn_prefill_tc5_tile_tokens tokens.
+// tiles of zk_attn_prefill_tc5_tile_tokens tokens.  part_o, part_ml (both or neither): the cross mode, see Params;
+// `out` is then not written.
 int zk_attn_prefill_tc5(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                         const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                         const int* page_table, int pt_stride, int n_tiles, int n_tokens, long long num_pages, int H,
-                        int Hkv, int hd, int page_size, float scale, int* status, cudaStream_t stream) {
+                        int Hkv, int hd, int page_size, float scale, int* status, float* part_o, float* part_ml,
+                        cudaStream_t stream) {
   if (n_tiles <= 0 || n_tokens <= 0) return 0;
+  if ((part_o == nullptr) != (part_ml == nullptr) || ((uintptr_t)part_o % 16) || (part_o && Hkv > 65535)) return ZK_EINVAL;
   if (!zk_attn_prefill_tc5_takes(H, Hkv, hd, page_size, 0) || !status || num_pages <= 0) return ZK_EINVAL;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16) return ZK_EINVAL;
   EncodeTiledFn fn = encode_fn();
@@ -408,9 +430,10 @@ int zk_attn_prefill_tc5(const void* q, const void* k_cache, const void* v_cache,
   p.out = (bf16*)out; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q; p.seq_start = seq_start;
   p.seq_slot = seq_slot; p.page_table = page_table; p.status = status;
   p.pt_stride = pt_stride; p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.gp = gp; p.scale = scale;
+  p.part_o = part_o; p.part_ml = part_ml;
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(n_tiles, Hkv * (G / gp));
+  dim3 grid(n_tiles, Hkv * (G / gp), part_o ? Hkv : 1);
   return zk_launch_dependent(attn_prefill_tc5_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p);
 }
 

@@ -4,48 +4,62 @@
 //
 // f_t in (lower, 1) the forget gate per head and channel, which also decides how much of v_t is written
 // (there is no key), q_t = silu(.), v_t plain.  A row of `qfv` holds the three projections of a token,
-// [q (H*d) | f (H*d) | v (H*e)], float32 as the contraction left them; the gate is
-// f = lower + (1 - lower) * sigmoid(z_f + bias).  Everything here is float32: gate, state, sums.
+// [q (H*d) | f (H*d) | v (H*e)], float32 as the contraction left them; hgrn2_gates_kernel turns the first
+// two parts, in place, into silu(q) and the gate f = lower + (1 - lower) * sigmoid(z_f + bias), once for
+// all the blocks of the recurrence that read them.  Everything here is float32: gate, state, sums.
 //
 // One kernel serves prompt steps and single-token steps.  A block owns one (sequence, head, 32 value columns)
 // and walks the sequence's tokens in order, from the state the step before left in `state[slot]` to the
 // state it leaves there.  Its eight warps split the d channels: warp w keeps rows [w*DPT, (w+1)*DPT) of the
 // 32 columns of S in registers (lane = column, so the state is read and written in whole lines), adds up its
-// part of o_t = sum_i S_t[i, c] q_t[i], and the parts of eight tokens at a time meet in shared memory, where
-// warp w sums those of token w in the order of the warps.  q and f of the next eight tokens are fetched into
-// registers while the current eight are worked on, and are turned into silu(q) and the gate on their way
-// into the other half of a double buffer.  The order of every sum is fixed by the layout alone, so a
+// part of o_t = sum_i S_t[i, c] q_t[i], and the parts of sixteen tokens at a time meet in shared memory, where
+// warp w sums those of tokens w and w + 8 in the order of the warps.  q and f of the next sixteen tokens are fetched into
+// registers while the current sixteen are worked on, and go into the other half of a double buffer.  The order of every sum is fixed by the layout alone, so a
 // sequence cut into steps gives the same bits as the whole.
 #include "common.cuh"
 #include <math.h>
 
-#define HG_TT 8            // tokens staged at once; also the warps of a block
 #define HG_R 8             // warps of a block, each with a stretch of the d channels
 #define HG_MAX_D 256
 
-template <int DPT>
+// In place on the rows of qfv: q <- silu(q), f <- lower + (1 - lower) * sigmoid(f + bias); v is left alone.
+__global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float* __restrict__ f_bias,
+                                   const float* __restrict__ lower, int n, int gate_dim) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const size_t total = (size_t)n * gate_dim;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gate_dim;
+    const int i = (int)(idx - t * gate_dim);
+    float* row = qfv + t * ld;
+    const float zq = row[i], zf = row[gate_dim + i] + f_bias[i], lo = lower[i];
+    row[i] = zq / (1.0f + expf(-zq));
+    row[gate_dim + i] = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-zf)));
+  }
+}
+
+// DPT: channels per warp; TT: tokens staged at once (sixteen, or eight where sixteen do not fit shared memory)
+template <int DPT, int TT>
 __global__ void __launch_bounds__(HG_R * 32)
-    hgrn2_scan_kernel(const float* __restrict__ qfv, int ld, const float* __restrict__ f_bias,
-                      const float* __restrict__ lower, float* __restrict__ state, long long state_stride,
+    hgrn2_scan_kernel(const float* __restrict__ qfv, int ld, float* __restrict__ state, long long state_stride,
                       float* __restrict__ o, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int H, int d,
                       int e) {
   constexpr int DM = HG_R * DPT;                                     // channels the block covers, >= d
-  constexpr int NL = (HG_TT * DM + HG_R * 32 - 1) / (HG_R * 32);     // q (and f) values a thread fetches per eight tokens
-  __shared__ __align__(16) float qs[2][HG_TT][DM];
-  __shared__ __align__(16) float fs[2][HG_TT][DM];
-  __shared__ float part[HG_TT][HG_R][32];
+  constexpr int NL = (TT * DM + HG_R * 32 - 1) / (HG_R * 32);     // q (and f) values a thread fetches per group of tokens
+  __shared__ __align__(16) float qs[2][TT][DM];
+  __shared__ __align__(16) float fs[2][TT][DM];
+  __shared__ float part[TT][HG_R][32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x, h = blockIdx.y;
   const int c = blockIdx.z * 32 + lane;
   const bool col = c < e;
   const int row0 = warp * DPT;
   // channels beyond d: q = 0 and f = 0 for good, so they add nothing
-  for (int i = tid; i < 2 * HG_TT * DM; i += HG_R * 32) {
+  for (int i = tid; i < 2 * TT * DM; i += HG_R * 32) {
     (&qs[0][0][0])[i] = 0.f;
     (&fs[0][0][0])[i] = 0.f;
   }
   __syncthreads();
-  zk_let_next_start();
   zk_wait_prior();   // qfv is the kernel before's result
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
   float* st = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
@@ -54,36 +68,40 @@ __global__ void __launch_bounds__(HG_R * 32)
   for (int k = 0; k < DPT; ++k) S[k] = (col && row0 + k < d) ? st[(size_t)(row0 + k) * e + c] : 0.f;
 
   const int off_f = H * d, off_v = 2 * H * d;
-  float rq[NL], rf[NL], v_cur[HG_TT], v_next[HG_TT];
+  float rq[NL], rf[NL], v_cur[TT], v_next[TT];
+  // where a thread's n-th value of a group comes from (relative to the group's first row) and goes to
+  int src[NL], dst[NL];
+#pragma unroll
+  for (int n = 0; n < NL; ++n) {
+    const int idx = tid + n * HG_R * 32;
+    const int tt = idx / d, i = idx - tt * d;
+    src[n] = tt < TT ? tt * ld + h * d + i : -1;
+    dst[n] = tt * DM + i;
+  }
   auto fetch = [&](int tb) {
-    const int nt = min(HG_TT, t1 - tb);
+    const int nt = min(TT, t1 - tb);
+    const float* base = qfv + (size_t)tb * ld;
 #pragma unroll
     for (int n = 0; n < NL; ++n) {
-      const int idx = tid + n * HG_R * 32;
-      const int tt = idx / d, i = idx - tt * d;
-      const bool ok = idx < nt * d;
-      const float* row = qfv + (size_t)(tb + (ok ? tt : 0)) * ld + h * d + (ok ? i : 0);
-      rq[n] = ok ? row[0] : 0.f;
-      rf[n] = ok ? row[off_f] : 0.f;
+      const bool ok = src[n] >= 0 && tid + n * HG_R * 32 < nt * d;
+      rq[n] = ok ? base[src[n]] : 0.f;
+      rf[n] = ok ? base[src[n] + off_f] : 0.f;
     }
 #pragma unroll
-    for (int tt = 0; tt < HG_TT; ++tt)
-      v_next[tt] = (col && tt < nt) ? qfv[(size_t)(tb + tt) * ld + off_v + h * e + c] : 0.f;
+    for (int tt = 0; tt < TT; ++tt)
+      v_next[tt] = (col && tt < nt) ? base[(size_t)tt * ld + off_v + h * e + c] : 0.f;
   };
   auto stage = [&](int buf, int tb) {
-    const int nt = min(HG_TT, t1 - tb);
+    const int nt = min(TT, t1 - tb);
 #pragma unroll
     for (int n = 0; n < NL; ++n) {
-      const int idx = tid + n * HG_R * 32;
-      if (idx < nt * d) {
-        const int tt = idx / d, i = idx - tt * d;
-        const float zq = rq[n], zf = rf[n] + f_bias[h * d + i], lo = lower[h * d + i];
-        qs[buf][tt][i] = zq / (1.0f + expf(-zq));
-        fs[buf][tt][i] = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-zf)));
+      if (src[n] >= 0 && tid + n * HG_R * 32 < nt * d) {
+        (&qs[buf][0][0])[dst[n]] = rq[n];
+        (&fs[buf][0][0])[dst[n]] = rf[n];
       }
     }
 #pragma unroll
-    for (int tt = 0; tt < HG_TT; ++tt) v_cur[tt] = v_next[tt];
+    for (int tt = 0; tt < TT; ++tt) v_cur[tt] = v_next[tt];
   };
 
   if (t0 < t1) {
@@ -92,48 +110,59 @@ __global__ void __launch_bounds__(HG_R * 32)
   }
   __syncthreads();
   int buf = 0;
-  for (int tb = t0; tb < t1; tb += HG_TT, buf ^= 1) {
-    const int nt = min(HG_TT, t1 - tb);
-    const bool more = tb + HG_TT < t1;
-    if (more) fetch(tb + HG_TT);       // under way while this group is worked on
+  for (int tb = t0; tb < t1; tb += TT, buf ^= 1) {
+    const int nt = min(TT, t1 - tb);
+    const bool more = tb + TT < t1;
+    if (more) fetch(tb + TT);       // under way while this group is worked on
+    auto token = [&](int tt) {
+      const float v = v_cur[tt];
+      float acc = 0.f;
+      if constexpr (DPT % 4 == 0) {
 #pragma unroll
-    for (int tt = 0; tt < HG_TT; ++tt) {
-      if (tt < nt) {
-        const float v = v_cur[tt];
-        float acc = 0.f;
-        if constexpr (DPT % 4 == 0) {
+        for (int k4 = 0; k4 < DPT; k4 += 4) {
+          const float4 f4 = *reinterpret_cast<const float4*>(&fs[buf][tt][row0 + k4]);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[buf][tt][row0 + k4]);
+          const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-          for (int k4 = 0; k4 < DPT; k4 += 4) {
-            const float4 f4 = *reinterpret_cast<const float4*>(&fs[buf][tt][row0 + k4]);
-            const float4 q4 = *reinterpret_cast<const float4*>(&qs[buf][tt][row0 + k4]);
-            const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              S[k4 + j] = fmaf(ff[j], S[k4 + j], fmaf(-ff[j], v, v));     // f S + (1 - f) v
-              acc = fmaf(S[k4 + j], qq[j], acc);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < DPT; ++k) {
-            const float f = fs[buf][tt][row0 + k];
-            S[k] = fmaf(f, S[k], fmaf(-f, v, v));
-            acc = fmaf(S[k], qs[buf][tt][row0 + k], acc);
+          for (int j = 0; j < 4; ++j) {
+            S[k4 + j] = fmaf(ff[j], S[k4 + j], fmaf(-ff[j], v, v));     // f S + (1 - f) v
+            acc = fmaf(S[k4 + j], qq[j], acc);
           }
         }
-        part[tt][warp][lane] = acc;
+      } else {
+#pragma unroll
+        for (int k = 0; k < DPT; ++k) {
+          const float f = fs[buf][tt][row0 + k];
+          S[k] = fmaf(f, S[k], fmaf(-f, v, v));
+          acc = fmaf(S[k], qs[buf][tt][row0 + k], acc);
+        }
+      }
+      part[tt][warp][lane] = acc;
+    };
+    if (nt == TT) {          // a whole group: no branch between the tokens, so their loads and sums interleave
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) token(tt);
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt)
+        if (tt < nt) token(tt);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int tt = warp; tt < TT; tt += HG_R) {
+      if (tt < nt && col) {
+        float sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < HG_R; ++r) sum += part[tt][r][lane];
+        o[(size_t)(tb + tt) * H * e + (size_t)h * e + c] = sum;
       }
     }
-    __syncthreads();
-    if (warp < nt && col) {
-      float sum = 0.f;
-#pragma unroll
-      for (int r = 0; r < HG_R; ++r) sum += part[warp][r][lane];
-      o[(size_t)(tb + warp) * H * e + (size_t)h * e + c] = sum;
-    }
-    if (more) stage(buf ^ 1, tb + HG_TT);
+    if (more) stage(buf ^ 1, tb + TT);
     __syncthreads();
   }
+  // The kernel behind this one may start only now: a block that waits for this long kernel to end would hold
+  // an SM's issue slots against it (measured: the recurrence ran at half its speed with the release at its top).
+  zk_let_next_start();
   if (col) {
 #pragma unroll
     for (int k = 0; k < DPT; ++k)
@@ -145,17 +174,26 @@ extern "C" {
 
 int zk_hgrn2_max_dim() { return HG_MAX_D; }
 
-// qfv float32 [n, >= 2*H*d + H*e] with rows `ld` floats apart; f_bias, lower float32 [H*d]; state float32, a
+// qfv float32 [n, >= 2*H*d + H*e] with rows `ld` floats apart, whose q and f parts are REPLACED by silu(q) and the
+// gate; f_bias, lower float32 [H*d]; state float32, a
 // slot's [H, d, e] block `state_stride` floats after the one before; o float32 [n, H*e]; cu_q [n_seqs + 1],
 // seq_slot [n_seqs].
-int zk_hgrn2_scan(const float* qfv, int ld, const float* f_bias, const float* lower, float* state, long long state_stride,
-                  float* o, const int* cu_q, const int* seq_slot, int n_seqs, int H, int d, int e, cudaStream_t stream) {
-  if (n_seqs <= 0) return 0;
+int zk_hgrn2_scan(float* qfv, int ld, const float* f_bias, const float* lower, float* state, long long state_stride,
+                  float* o, const int* cu_q, const int* seq_slot, int n, int n_seqs, int H, int d, int e, cudaStream_t stream) {
+  if (n_seqs <= 0 || n <= 0) return 0;
   if (H <= 0 || d <= 0 || e <= 0 || d > HG_MAX_D || ld < 2 * H * d + H * e || !f_bias || !lower) return ZK_EINVAL;
+  {
+    const size_t total = (size_t)n * H * d;
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int rc = zk_launch_dependent(hgrn2_gates_kernel, dim3(blocks), dim3(threads), 0, stream, qfv, ld, f_bias, lower, n, H * d);
+    if (rc != 0) return rc;
+  }
   dim3 grid(n_seqs, H, (e + 31) / 32);
-#define ZK_HG(DP)                                                                                                     \
-  return zk_launch_dependent(hgrn2_scan_kernel<DP>, grid, dim3(HG_R * 32), 0, stream, qfv, ld, f_bias, lower, state, \
-                             state_stride, o, cu_q, seq_slot, H, d, e)
+#define ZK_HG(DP)                                                                                                    \
+  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 16 ? 8 : 16)>, grid, dim3(HG_R * 32), 0, stream, (const float*)qfv, ld, \
+                             state, state_stride, o, cu_q, seq_slot, H, d, e)
   const int dpt = (d + HG_R - 1) / HG_R;
   if (dpt <= 1) ZK_HG(1);
   if (dpt <= 2) ZK_HG(2);

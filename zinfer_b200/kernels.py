@@ -39,7 +39,7 @@ _SIGNATURES = {
         "zk_norm_shift": "pppplppppiiifiip",
     },
     "hgrn2": {
-        "zk_hgrn2_scan": "pippplpppiiiip",
+        "zk_hgrn2_scan": "pippplpppiiiiip",
         "zk_hgrn2_max_dim": "",
     },
     "seqconv": {
@@ -86,7 +86,7 @@ _SIGNATURES = {
         "zk_attn_prefill_tile_tokens": "ii",
     },
     "attention_prefill_tc5": {
-        "zk_attn_prefill_tc5": "pppppppppp" + "iii" + "l" + "iiii" + "f" + "pp",
+        "zk_attn_prefill_tc5": "pppppppppp" + "iii" + "l" + "iiii" + "f" + "p" + "pp" + "p",
         "zk_attn_prefill_tc5_takes": "iiiii",
         "zk_attn_prefill_tc5_tile_tokens": "ii",
     },
@@ -365,7 +365,8 @@ def hgrn2_scan(qfv: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, sta
                n_seqs: int, n_heads: int, dim: int, value_dim: int) -> torch.Tensor:
     """Per head S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t over each sequence's tokens, from the state
     the step before left to the state this one leaves.  qfv float32 [n, 2*H*d + H*e], a row [q | f | v] as the
-    projections gave them (q <- silu, f <- lower + (1 - lower) * sigmoid(f + f_bias) here); state float32
+    projections gave them; its q and f parts are overwritten (q <- silu(q), f <- lower + (1 - lower) *
+    sigmoid(f + f_bias), by a kernel of their own before the recurrence); state float32
     [slots, H*d*e] (rows `state.stride(0)` apart), a slot's values ordered [H, d, e]; returns o float32 [n, H*e]."""
     H, d, e = n_heads, dim, value_dim
     _need(qfv, "qfv", torch.float32, (None, 2 * H * d + H * e))
@@ -378,7 +379,7 @@ def hgrn2_scan(qfv: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, sta
         _need(t, nm, torch.int32)
     o = torch.empty((qfv.shape[0], H * e), dtype=torch.float32, device=qfv.device)
     _check(_fn("hgrn2", "zk_hgrn2_scan")(_ptr(qfv), qfv.stride(0), _ptr(f_bias), _ptr(lower), _ptr(state), state.stride(0),
-                                         _ptr(o), _ptr(cu_q), _ptr(seq_slot), n_seqs, H, d, e, _stream()), "hgrn2_scan")
+                                         _ptr(o), _ptr(cu_q), _ptr(seq_slot), qfv.shape[0], n_seqs, H, d, e, _stream()), "hgrn2_scan")
     return o
 
 
@@ -985,10 +986,10 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
     taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
-    are mixed across the heads after the softmax (`talking`) by the same three."""
+    are mixed across the heads after the softmax (`talking`) by those three and the tcgen05 prompt kernel."""
     same_width = value_dim is None or value_dim == head_dim
     if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
-        if (not single_token and window <= 0 and not biased and not talking and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+        if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
@@ -1013,7 +1014,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     row if it is not head_dim.  `bias` = (r1, r2), float32 [H] each: r1_h * ln(1 + r2_h * (i - j)) is taken
     off the scaled score of query position i and key position j.  Both are the general kernel's.
     `talk` float32 [H, H]: after the softmax head h's weights become sum_g talk[h, g] * (head g's weights), and
-    head h applies them to the values of its own key/value head (general kernel and the two mma.sync kernels:
+    head h applies them to the values of its own key/value head (every kernel but the one-lane-per-key one:
     every head's weights meet every key/value head's values, and a merge kernel mixes the results)."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * head_dim))
     n = q.shape[0]
@@ -1025,7 +1026,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             _need(b, nm, torch.float32, (n_heads,))
     if talk is not None:
         _need(talk, "talk", torch.float32, (n_heads, n_heads))
-        if kind not in (None, "general", "prompt_tc", "single_token_tc"):
+        if kind not in (None, "general", "prompt_tc5", "prompt_tc", "single_token_tc"):
             raise KernelError(f"attention: the '{kind}' kernel mixes no weights across heads")
     if vd != head_dim and kind not in (None, "general"):
         raise KernelError(f"attention: the '{kind}' kernel takes no value width of its own")
@@ -1057,9 +1058,10 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention_prefill_tc5", "zk_attn_prefill_tc5")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, k_cache.shape[0],
-            n_heads, n_kv, head_dim, page_size, scale, _ptr(status_word(q.device)), _stream()),
+            n_heads, n_kv, head_dim, page_size, scale, _ptr(status_word(q.device)),
+            _ptr(part_o) if talk is not None else None, _ptr(part_ml) if talk is not None else None, _stream()),
             "attention (prompt, tcgen05)")
-        return out
+        return out if talk is None else _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, 1)
     if kind == "prompt_tc":
         if q.dtype != torch.bfloat16 or not _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim,
                                                    page_size):
