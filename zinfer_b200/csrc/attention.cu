@@ -586,25 +586,27 @@ __global__ void attn_merge_talk_kernel(const float* __restrict__ part_o, const f
     if (lane + 32 * i < vd) out[((size_t)t * H + h) * vd + lane + 32 * i] = from_f32<T>(acc[i]);
 }
 
-// The same with one block per token: the token's H * Hkv merged and normalised sums are first laid down in
-// shared memory (a warp per row, the splits in ascending order), then every output value adds its H terms
-// in the order of g.  Each partial sum is read once, in whole lines.
+// The same with one block per (token, key/value head c): the H sums of that value head, merged over the splits
+// and normalised, are first laid down in shared memory (a warp per row, the splits in ascending order), then
+// every output value of the heads that belong to c adds its H terms in the order of g.  Each partial sum is
+// read once, in whole lines.
 template <typename T>
 __global__ void __launch_bounds__(256)
     attn_merge_talk_token_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                  const float* __restrict__ talk, T* __restrict__ out, int n_tokens, int H, int Hkv, int vd,
                                  int num_splits) {
   extern __shared__ float mt_smem[];
-  float* A = mt_smem;                      // [H * Hkv][vd]
-  float* Tm = A + (size_t)H * Hkv * vd;    // [H][H]
+  float* A = mt_smem;                      // [H][vd]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-  for (int i = tid; i < H * H; i += blockDim.x) Tm[i] = talk[i];
+  const int per = H / Hkv;
+  const int t = blockIdx.x, c = blockIdx.y;
+  float* Tm = A + (size_t)H * vd;          // [per][H]: the rows of `talk` of this block's heads
+  for (int i = tid; i < per * H; i += blockDim.x) Tm[i] = talk[(size_t)c * per * H + i];
   zk_let_next_start();
   zk_wait_prior();
-  const int t = blockIdx.x;
   const size_t rows_per_split = (size_t)n_tokens * H * Hkv;
-  for (int r = warp; r < H * Hkv; r += nw) {
-    const size_t row = (size_t)t * H * Hkv + r;
+  for (int g = warp; g < H; g += nw) {
+    const size_t row = ((size_t)t * H + g) * Hkv + c;
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[((size_t)s * rows_per_split + row) * 2]);
     float L = 0.f, og[8];
@@ -623,16 +625,14 @@ __global__ void __launch_bounds__(256)
     const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      if (lane + 32 * i < vd) A[(size_t)r * vd + lane + 32 * i] = og[i] * inv;
+      if (lane + 32 * i < vd) A[(size_t)g * vd + lane + 32 * i] = og[i] * inv;
   }
   __syncthreads();
-  const int per = H / Hkv;
-  for (int idx = tid; idx < H * vd; idx += blockDim.x) {
-    const int h = idx / vd, d = idx - h * vd;
-    const int c = h / per;
+  for (int idx = tid; idx < per * vd; idx += blockDim.x) {
+    const int hl = idx / vd, d = idx - hl * vd;
     float acc = 0.f;
-    for (int g = 0; g < H; ++g) acc = fmaf(Tm[h * H + g], A[((size_t)g * Hkv + c) * vd + d], acc);
-    out[((size_t)t * H + h) * vd + d] = from_f32<T>(acc);
+    for (int g = 0; g < H; ++g) acc = fmaf(Tm[hl * H + g], A[(size_t)g * vd + d], acc);
+    out[((size_t)t * H + c * per + hl) * vd + d] = from_f32<T>(acc);
   }
 }
 
@@ -783,15 +783,15 @@ int zk_attn_merge_talk(const float* part_o, const float* part_ml, const float* t
                        int vd, int num_splits, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || vd <= 0 || vd > ATT_MAX_HD || num_splits < 1 || !talk) return ZK_EINVAL;
-  const size_t smem = ((size_t)H * Hkv * vd + (size_t)H * H) * sizeof(float);
-  if (smem <= 200 * 1024 && (dtype == ZK_F32 || dtype == ZK_BF16)) {
+  const size_t smem = ((size_t)H * vd + (size_t)(H / Hkv) * H) * sizeof(float);
+  if (smem <= 200 * 1024 && Hkv <= 65535 && (dtype == ZK_F32 || dtype == ZK_BF16)) {
     if (dtype == ZK_F32) {
       auto kern = attn_merge_talk_token_kernel<float>;
       if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
       }
-      return zk_launch_dependent(kern, dim3(n_tokens), dim3(256), smem, stream, part_o, part_ml, talk, (float*)out, n_tokens,
+      return zk_launch_dependent(kern, dim3(n_tokens, Hkv), dim3(256), smem, stream, part_o, part_ml, talk, (float*)out, n_tokens,
                                  H, Hkv, vd, num_splits);
     }
     auto kern = attn_merge_talk_token_kernel<bf16>;
@@ -799,7 +799,7 @@ int zk_attn_merge_talk(const float* part_o, const float* part_ml, const float* t
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    return zk_launch_dependent(kern, dim3(n_tokens), dim3(256), smem, stream, part_o, part_ml, talk, (bf16*)out, n_tokens, H,
+    return zk_launch_dependent(kern, dim3(n_tokens, Hkv), dim3(256), smem, stream, part_o, part_ml, talk, (bf16*)out, n_tokens, H,
                                Hkv, vd, num_splits);
   }
   const int warps = 4;

@@ -39,6 +39,9 @@ struct Args {
   const bf16* W;         // [rows, K]
   void* C;
   const float* bias;     // per weight row, or null
+  const float* col_scale;  // EPI_PLAIN: per output column, applied to the sum (after bias and activation) before it is
+                           // stored or added to C; or null
+  int act;               // EPI_PLAIN: 0 none, 1 the square of relu, applied to the sum (after the bias)
   int M, N, K, ldx, ldw, ldc, accumulate;
   // NORM_SCALED: X holds bfloat16(x * norm weight); ssq_in [M, ssq_parts] are partial sums of x^2
   const float* ssq_in;
@@ -365,6 +368,11 @@ __global__ void __launch_bounds__(WARPS * 32, skinny_min_blocks(WARPS, NT, EPI))
       if (in) {
         v = total(nl, m);
         if (a.bias) v += a.bias[n];
+        if (a.act == 1) {
+          v = fmaxf(v, 0.f);
+          v *= v;
+        }
+        if (a.col_scale) v = __fmul_rn(a.col_scale[n], v);    // rounded before the sum, as the separate kernel does
         TC* dst = C + (size_t)m * a.ldc + n;
         if (a.accumulate) v += to_f32(*dst);
         *dst = from_f32<TC>(v);
@@ -550,13 +558,17 @@ int zk_gemm_skinny_fused_max_m() { return 16; }
 // ssq_in [M, ssq_parts] (or null): X is bfloat16(x * norm weight) and the sums are scaled by
 // 1 / sqrt(sum(ssq_in[m]) / K + eps) (M <= 16).  emit_x (or null; M <= 16, float32 C, no fused norm):
 // also writes emit_x [M, N] = bfloat16(C * emit_w) and emit_ssq [M, ceil(N / 16)] for the next norm.
+// act 1: the sum (with its bias) is replaced by the square of its positive part; col_scale [N] (or null): the
+// result is multiplied by a number per column before it is stored or added to C (a layer scale).
 int zk_gemm_skinny(const void* X, const float* Xf, const float* norm_w, float eps, const void* W, void* C,
                    const float* bias, int M, int N, int K, int ldx, int ldw, int ldc, int out_dtype, int accumulate,
                    const float* ssq_in, int ssq_parts, const float* emit_w, void* emit_x, float* emit_ssq,
-                   cudaStream_t stream) {
+                   const float* col_scale, int act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (act < 0 || act > 1 || (emit_x && (col_scale || act))) return ZK_EINVAL;
   Args a{};
   a.X = (const bf16*)X; a.Xf = Xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.C = C; a.bias = bias;
+  a.col_scale = col_scale; a.act = act;
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldc = ldc; a.accumulate = accumulate;
   a.ssq_in = Xf ? nullptr : ssq_in; a.ssq_parts = ssq_parts;
   a.emit_w = emit_w; a.emit_x = (bf16*)emit_x; a.emit_ssq = emit_ssq;

@@ -56,7 +56,7 @@ _SIGNATURES = {
         "zk_gemm_simt": "ppppiiiiiiiiip",
     },
     "gemm_skinny": {
-        "zk_gemm_skinny": "pppfpppiiiiiiii" + "pippp" + "p",
+        "zk_gemm_skinny": "pppfpppiiiiiiii" + "pippp" + "pi" + "p",
         "zk_gemm_skinny_swiglu": "pppfppiiiiii" + "pi" + "p",
         "zk_gemm_skinny_conv": "pppfppppppp" + "iiiiiiil" + "pi" + "p",
         "zk_gemm_skinny_max_m": "",
@@ -726,8 +726,11 @@ def gemm_skinny_emits(a, out: Optional[torch.Tensor]) -> bool:
 
 def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
                 accumulate: bool = False, bias: Optional[torch.Tensor] = None,
-                emit: Optional[NormEmit] = None) -> torch.Tensor:
+                emit: Optional[NormEmit] = None, col_scale: Optional[torch.Tensor] = None,
+                act: Optional[str] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) for a [M <= 64, K] on the tensor cores, every weight read once.
+    `act` ("relu_squared") is applied to the sums, then `col_scale` (float32 [N], one number per column)
+    multiplies them, before they are stored or added to `out`.
     With a NormInput the RMSNorm of the rows is applied inside the kernel; with a ScaledInput the
     sums are scaled by the rows' 1/rms.  `emit` (see `gemm_skinny_emits`) is filled for the norm
     that reads `out` next."""
@@ -743,6 +746,12 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtyp
     _need(out, "out", (torch.float32, torch.bfloat16), (M, N))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
+    if act not in (None, "relu_squared"):
+        raise KernelError(f"gemm_skinny: no epilogue for the activation {act!r}")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, (N,))
+    if emit is not None and (col_scale is not None or act is not None):
+        raise KernelError("gemm_skinny: the next norm's inputs are not written behind a scale or an activation")
     if emit is not None:
         if not gemm_skinny_emits(a, out):
             raise KernelError("gemm_skinny: the norm's inputs are written for at most 16 bfloat16 rows "
@@ -754,7 +763,8 @@ def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtyp
                                                 w.stride(0), out.stride(0), dtype_code(out.dtype),
                                                 1 if accumulate else 0, ssq, ssq_parts,
                                                 _ptr(emit.weight) if emit else None, _ptr(emit.xw) if emit else None,
-                                                _ptr(emit.ssq) if emit else None, _stream()), "gemm_skinny")
+                                                _ptr(emit.ssq) if emit else None, _ptr(col_scale), 1 if act else 0,
+                                                _stream()), "gemm_skinny")
     return out
 
 

@@ -15,10 +15,13 @@ feed-forward whatever the model says runs next (`forward_chained`).
 Two options other designs use: no feed-forward at all (`ffn` and `ffn_norm` None: the block is its first
 sum alone), and layer scale: a sublayer's result is multiplied by a learned vector (`mixer_scale_name`,
 `ffn_scale_name`, one number per channel) before it is summed, x += s * Mixer(norm(x)).  A scaled sublayer
-writes into a float32 buffer and `kernels.scale_add` sums it in, so nothing is prepared for the next norm."""
+that sums through `linear` is handed a `ScaledSink` (rows and scale: the contraction applies the scale in its
+epilogue where it can); any other writes into a float32 buffer and `kernels.scale_add` sums it in.  Nothing is
+prepared for the next norm behind a scale."""
 from __future__ import annotations
 
 from .base import BLOCKS, Block, FeedForward, Mixer, Norm, WeightSpec
+from .linear import ScaledSink
 
 
 class PreNormBlock(Block):
@@ -55,7 +58,10 @@ class PreNormBlock(Block):
         from .. import kernels
         import torch
         mid = None
-        if self.mixer_scale is not None:
+        if self.mixer_scale is not None and getattr(self.mixer, "sums_through_linear", False):
+            self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry),
+                               ScaledSink(x, self.mixer_scale), True)
+        elif self.mixer_scale is not None:
             m = torch.empty_like(x)
             self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry), m, False)
             kernels.scale_add(m, self.mixer_scale, x)
@@ -64,6 +70,9 @@ class PreNormBlock(Block):
             self.mixer.forward(ctx, call, normed_for(self.mixer, self.mixer_norm, ctx, x, entry),
                                x if mid is None else mid, True)
         if self.ffn is None:
+            return None
+        if self.ffn_scale is not None and getattr(self.ffn, "sums_through_linear", False):
+            self.ffn.forward(ctx, normed_for(self.ffn, self.ffn_norm, ctx, x, mid), ScaledSink(x, self.ffn_scale), True)
             return None
         if self.ffn_scale is not None:
             m = torch.empty_like(x)

@@ -61,6 +61,7 @@ class ActMlp(FeedForward):
     """Ungated feed-forward: out (+)= act(xn W_up^T) W_down^T, act one of `kernels.ACTIVATIONS`
     ("gelu" is the exact erf form), evaluated in float32."""
 
+    takes_pending_norm = True
     sums_through_linear = True
 
     def __init__(self, hidden: int, ffn_dim: int, up_name: str, down_name: str, act: str = "gelu"):
@@ -77,8 +78,7 @@ class ActMlp(FeedForward):
         self.w_up, self.w_down = weights[self.up_name], weights[self.down_name]
 
     def forward(self, ctx, xn, out, accumulate):
-        u = linear(xn, self.w_up)
-        linear(kernels.activation(u, self.act, out=u), self.w_down, out=out, accumulate=accumulate)
+        linear(linear(xn, self.w_up, act=self.act), self.w_down, out=out, accumulate=accumulate)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -56,6 +56,15 @@ class ResidualSink:
         self.emit: Optional["kernels.NormEmit"] = None
 
 
+class ScaledSink:
+    """The float32 residual rows as the target of an accumulating contraction whose result is first multiplied
+    by a learned number per column (a layer scale): rows[:, n] += scale[n] * (a @ w.T)[:, n].  A kernel that can
+    applies the scale in its epilogue; otherwise the product goes to a buffer and `kernels.scale_add` sums it in."""
+
+    def __init__(self, rows: torch.Tensor, scale: torch.Tensor):
+        self.rows, self.scale = rows, scale
+
+
 FUSION_GROUP = 16     # rows per part and group in the interleaved weight layouts of the fused kernels
 
 
@@ -118,10 +127,14 @@ def fused_input(a: Union[torch.Tensor, NormedRows], w: torch.Tensor, need_fused_
 
 
 def linear(a: Union[torch.Tensor, NormedRows], w: torch.Tensor,
-           out: Union[torch.Tensor, ResidualSink, None] = None, out_dtype=None,
-           accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Union[torch.Tensor, ResidualSink, "ScaledSink", None] = None, out_dtype=None,
+           accumulate: bool = False, bias: Optional[torch.Tensor] = None, act: Optional[str] = None) -> torch.Tensor:
     """a [M, K] and w [N, K] in the run dtype; result [M, N] in `out_dtype` (default: run dtype),
-    or added into `out` when `accumulate`."""
+    or added into `out` when `accumulate`.  `act` names an activation (`kernels.ACTIVATIONS`) applied to the
+    result; `out` may be a `ScaledSink`: the result is multiplied by its scale per column and added to its
+    rows.  Both run in the contraction's epilogue where the kernel has one, else as kernels of their own."""
+    if isinstance(out, ScaledSink) or act is not None:
+        return _linear_with_epilogue(a, w, out, out_dtype, accumulate, bias, act)
     sink = None
     if isinstance(out, ResidualSink):
         sink, out = out, out.rows
@@ -131,3 +144,30 @@ def linear(a: Union[torch.Tensor, NormedRows], w: torch.Tensor,
         if y is not None:
             return y
     return kernels.gemm_simt(as_tensor(a), w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias)
+
+
+FUSED_EPILOGUE_MAX_ROWS = 16      # above, the tcgen05 contractions are the faster ones and the epilogue runs as a kernel
+
+
+def _linear_with_epilogue(a, w, out, out_dtype, accumulate, bias, act):
+    scale = None
+    if isinstance(out, ScaledSink):
+        if not accumulate:
+            raise ValueError("a scaled sink is summed into: accumulate must be set")
+        scale, out = out.scale, out.rows
+    if isinstance(out, ResidualSink):
+        out = out.rows
+    if w.dtype == torch.bfloat16 and (act is None or act == "relu_squared") and a.shape[0] <= FUSED_EPILOGUE_MAX_ROWS:
+        x = fused_input(a, w)
+        if x is not None:                # few rows: activation and scale in the weight-streaming kernel's epilogue
+            return kernels.gemm_skinny(x, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
+                                       col_scale=scale, act=act)
+    if scale is None:
+        if accumulate:
+            raise ValueError("an activated product is not summed into rows without a scale")
+        y = linear(a, w, out=out, out_dtype=out_dtype, bias=bias)
+        return kernels.activation(y, act, out=y)
+    y = linear(a, w, out_dtype=torch.float32, bias=bias)
+    if act is not None:
+        kernels.activation(y, act, out=y)
+    return kernels.scale_add(y, scale, out)

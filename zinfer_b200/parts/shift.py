@@ -35,6 +35,10 @@ class TokenShift(Mixer):
     def capture_safe(self):
         return self.inner.capture_safe
 
+    @property
+    def sums_through_linear(self):
+        return getattr(self.inner, "sums_through_linear", False)
+
     def parts(self):
         return [self.inner]
 
