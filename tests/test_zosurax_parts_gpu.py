@@ -41,6 +41,25 @@ def test_layer_scale_pass_input_and_squared_relu(k, dim):
         close(k.activation(z.to(dtype).cuda(), "relu_squared"), np.maximum(f64(z), 0) ** 2, dtype, "squared relu")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [3, 16, 40, 200])
+@pytest.mark.parametrize("N,K", [(256, 128), (96, 72), (512, 256)])
+def test_contractions_with_an_activation_or_a_scaled_sum(k, dtype, rows, N, K):
+    """`linear(act=...)` and `linear(out=ScaledSink(...))` whichever kernel runs the product: the few-row kernel's
+    epilogue, the persistent tcgen05 forms' epilogue, or kernels of their own behind any other contraction."""
+    from zinfer_b200.parts.linear import ScaledSink, linear
+    a, w = rnd((rows, K), 10, dtype), rnd((N, K), 11, dtype, K ** -0.5)
+    x, sc = rnd((rows, N), 12, torch.float32), rnd((N,), 13, torch.float32)
+    y = f64(a) @ f64(w).T
+    got = linear(a.to(dtype).cuda(), w.to(dtype).cuda(), act="relu_squared")
+    assert got.dtype == dtype
+    close(got, np.maximum(y, 0) ** 2, dtype, "activated")
+    rows_dev = x.clone().cuda()
+    linear(a.to(dtype).cuda(), w.to(dtype).cuda(), out=ScaledSink(rows_dev, sc.cuda()), accumulate=True)
+    ref = f64(x) + y * f64(sc)
+    close(rows_dev, ref, dtype, "scaled sum")
+
+
 # ------------------------------------------------------------------------------- token shift
 
 class Passthrough:

@@ -1,4 +1,4 @@
-"""zinfer_b200: a small, whole inference library for one B200 (sm_100a): LFM2 and Ponusun models.
+"""zinfer_b200: a small, whole inference library for one B200 (sm_100a): LFM2, Ponusun and Zosurax models.
 
     import zinfer_b200 as z
     model  = z.load("path/to/folder", dtype="bf16")          # or z.random(config, seed=0, dtype="fp32")
@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from . import models as _models  # noqa: F401  (registers the architectures)
-from .config import ConfigError, Lfm2Config, PonusunConfig, config_from_dict, config_from_folder
+from .config import ConfigError, Lfm2Config, PonusunConfig, ZosuraxConfig, config_from_dict, config_from_folder
 from .engine.engine import Engine, StepError
 from .engine.generate import GenerationResult, Stats
 from .sampling import SamplingParams

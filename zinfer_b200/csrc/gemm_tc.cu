@@ -62,6 +62,10 @@ struct Params {
   // Grouped products (normal mode; one tile per block, or persistent single blocks): W is [groups, N, K] and the
   // 128 rows of token tile t are multiplied with the matrix of group tile_group[t]; null = one matrix for all rows.
   const int* tile_group;
+  // Persistent forms only: act 1 replaces a sum (with its bias) by the square of its positive part; col_scale [N]
+  // (or null) multiplies the result per column before it is stored or added to C (a layer scale).
+  const float* col_scale;
+  int act;
 };
 
 // q[j] of every lane, j < T (T = 4, 8 or 16): the sums over the warp's 32 lanes, T - 1 + log2(32 / T)
@@ -718,6 +722,18 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] += b[j];
           }
+          if (p.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float r = fmaxf(v[j], 0.f);
+              v[j] = r * r;
+            }
+          }
+          if (p.col_scale) {
+            const float* sc = p.col_scale + b_tile * BN + g * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(sc[j], v[j]);
+          }
           stage_row<TC, 32>(row, lane, part * (32 * (int)sizeof(TC) / 16), v);
         }
         if (part == groups_per_piece - 1) {
@@ -871,7 +887,17 @@ int normal_form(int M, int N) {
 
 extern "C" {
 
+// Whether a product of these sizes runs a persistent form, whose epilogue takes an activation and a scale per column.
+int zk_gemm_tc_fuses_epilogue(int M, int N, int ldc, int out_dtype, int accumulate) {
+  const bool f32 = out_dtype == ZK_F32;
+  if (M <= 64 || (out_dtype != ZK_F32 && out_dtype != ZK_BF16)) return 0;
+  const bool tma_out = (ldc * (f32 ? 4 : 2)) % 16 == 0 && (f32 || !accumulate);
+  const int form = tma_out ? normal_form(M, N) : 0;
+  return form == 512 || form == 256;
+}
+
 // X [M, K], W [N, K] bfloat16, K % 8 == 0, rows 16-byte aligned; C [M, N] bfloat16 or float32.
+// col_scale [N] / act: see Params; taken only where zk_gemm_tc_fuses_epilogue says so.
 // M <= 64 runs swapped (weights on the 128-row side) with K cut into `splits` parts (rounded down
 // to 1, 2, 4 or 8: a cluster's size); larger M runs normal and ignores splits.  With `swiglu`
 // W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2] receives
@@ -881,9 +907,12 @@ extern "C" {
 // emit_ssq [M, ceil(N / 32)] as the sums of C^2 over 32 columns.
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
                int out_dtype, int accumulate, int splits, int swiglu, const float* ssq_in, int ssq_parts, float eps,
-               const float* emit_w, void* emit_x, float* emit_ssq, int* status, cudaStream_t stream) {
+               const float* emit_w, void* emit_x, float* emit_ssq, int* status, const float* col_scale, int act,
+               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((ssq_in || emit_x) && M > 64) return ZK_EINVAL;
+  if ((col_scale || act) && (act < 0 || act > 1 || swiglu || !zk_gemm_tc_fuses_epilogue(M, N, ldc, out_dtype, accumulate)))
+    return ZK_EINVAL;
   if (ssq_in && ssq_parts <= 0) return ZK_EINVAL;
   if (emit_x && (!emit_w || !emit_ssq || swiglu || out_dtype != ZK_F32)) return ZK_EINVAL;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldc < (swiglu ? N / 2 : N) || !status) return ZK_EINVAL;
@@ -895,6 +924,7 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.accumulate = accumulate; p.splits = 1; p.swiglu = swiglu;
   p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.eps = eps;
   p.emit_w = emit_w; p.emit_x = (bf16*)emit_x; p.emit_ssq = emit_ssq;
+  p.col_scale = col_scale; p.act = act;
   CUtensorMap ma, mb, mc;
   const bool f32 = out_dtype == ZK_F32;
   if (M > 64) {

@@ -63,7 +63,8 @@ _SIGNATURES = {
         "zk_gemm_skinny_fused_max_m": "",
     },
     "gemm_tc": {
-        "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "pp",
+        "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "p" + "pi" + "p",
+        "zk_gemm_tc_fuses_epilogue": "iiiii",
         "zk_gemm_tc_force_form": "i",
         "zk_gemm_tc_grouped": "pppiiiiiiiippp",
     },
@@ -541,8 +542,10 @@ def gemm_tc_emits(a, out: Optional[torch.Tensor]) -> bool:
 
 def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
             accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1,
-            swiglu: bool = False, emit: Optional["NormEmit"] = None) -> torch.Tensor:
+            swiglu: bool = False, emit: Optional["NormEmit"] = None, col_scale: Optional[torch.Tensor] = None,
+            act: Optional[str] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
+    `act` ("relu_squared") and `col_scale` (float32 [N]) as in `gemm_skinny`, where `gemm_tc_fuses` says so.
     More than 64 rows: persistent blocks on 256-wide tiles when N is a multiple of 256 (pairs of
     blocks with tcgen05.mma.cta_group::2 above 128 rows, TMA stores), else one 128 x 128 tile of
     tokens x weight rows per block.  Up to 64 rows: the weights take
@@ -569,6 +572,12 @@ def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=No
     _need(out, "out", (torch.float32, torch.bfloat16), (M, n_out))
     if bias is not None:
         _need(bias, "bias", torch.float32, (N,))
+    if act not in (None, "relu_squared"):
+        raise KernelError(f"gemm_tc: no epilogue for the activation {act!r}")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, (N,))
+    if (col_scale is not None or act is not None) and (swiglu or emit is not None or not gemm_tc_fuses(a, w, out, accumulate)):
+        raise KernelError("gemm_tc: an activation or a scale per column is taken by the persistent forms only")
     if emit is not None:
         if not gemm_tc_emits(a, out) or swiglu:
             raise KernelError("gemm_tc: the norm's inputs are written for at most 64 rows summed into contiguous "
@@ -580,9 +589,19 @@ def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=No
                                         out.stride(0), dtype_code(out.dtype), 1 if accumulate else 0, splits,
                                         1 if swiglu else 0, ssq, ssq_parts, eps,
                                         _ptr(emit.weight) if emit else None, _ptr(emit.xw) if emit else None,
-                                        _ptr(emit.ssq) if emit else None, _ptr(status_word(a.device)), _stream()),
+                                        _ptr(emit.ssq) if emit else None, _ptr(status_word(a.device)), _ptr(col_scale),
+                                        1 if act else 0, _stream()),
            "gemm_tc")
     return out
+
+
+def gemm_tc_fuses(a, w: torch.Tensor, out: Optional[torch.Tensor], accumulate: bool, out_dtype=None) -> bool:
+    """Whether `gemm_tc` of these operands runs a form whose epilogue takes `act` and `col_scale`."""
+    if isinstance(a, ScaledInput) or not gemm_tc_takes(a, w, out):
+        return False
+    dt = out.dtype if out is not None else (out_dtype or torch.bfloat16)
+    ldc = out.stride(0) if out is not None else w.shape[0]
+    return bool(_fn("gemm_tc", "zk_gemm_tc_fuses_epilogue")(a.shape[0], w.shape[0], ldc, dtype_code(dt), 1 if accumulate else 0))
 
 
 GEMM_TC_GROUP_ROWS = 128       # rows per token tile of a grouped product

@@ -162,6 +162,11 @@ def _linear_with_epilogue(a, w, out, out_dtype, accumulate, bias, act):
         if x is not None:                # few rows: activation and scale in the weight-streaming kernel's epilogue
             return kernels.gemm_skinny(x, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias,
                                        col_scale=scale, act=act)
+    if w.dtype == torch.bfloat16 and (act is None or act == "relu_squared") and a.shape[0] > kernels.GEMM_TC_SWAPPED_MAX_M:
+        t = as_tensor(a)
+        if kernels.gemm_tc_fuses(t, w, out, accumulate, out_dtype):   # many rows: the persistent tcgen05 forms' epilogue
+            return kernels.gemm_tc(t, w, out=out, out_dtype=out_dtype, accumulate=accumulate, bias=bias, col_scale=scale,
+                                   act=act)
     if scale is None:
         if accumulate:
             raise ValueError("an activated product is not summed into rows without a scale")
