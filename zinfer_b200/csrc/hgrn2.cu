@@ -2,8 +2,8 @@
 //
 //     S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,        o_t = S_t^T q_t,
 //
-// f_t in (lower, 1) the forget gate per head and channel, which also decides how much of v_t is written
-// (there is no key), q_t = silu(.), v_t plain.  A row of `qfv` holds the three projections of a token,
+// f_t in (lower, 1) the forget gate per head and channel; 1 - f_t is the share of v_t that enters the state
+// (no key projection), q_t = silu(.), v_t plain.  A row of `qfv` holds the three projections of a token,
 // [q (H*d) | f (H*d) | v (H*e)], float32 as the contraction left them; hgrn2_gates_kernel turns the first
 // two parts, in place, into silu(q) and the gate f = lower + (1 - lower) * sigmoid(z_f + bias), once for
 // all the blocks of the recurrence that read them.  Everything here is float32: gate, state, sums.
@@ -55,11 +55,13 @@ __global__ void __launch_bounds__(HG_R * 32)
   const bool col = c < e;
   const int row0 = warp * DPT;
   // channels beyond d: q = 0 and f = 0 for good, so they add nothing
-  for (int i = tid; i < 2 * TT * DM; i += HG_R * 32) {
-    (&qs[0][0][0])[i] = 0.f;
-    (&fs[0][0][0])[i] = 0.f;
+  if (d < DM) {
+    for (int i = tid; i < 2 * TT * DM; i += HG_R * 32) {
+      (&qs[0][0][0])[i] = 0.f;
+      (&fs[0][0][0])[i] = 0.f;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   zk_wait_prior();   // qfv is the kernel before's result
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
   float* st = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;

@@ -1,4 +1,5 @@
-"""HGRN2 mixer: linear attention whose forget gate also decides what is written.
+"""HGRN2 mixer: a gated linear recurrence over a matrix state; the gate that decays the state also sets how much
+of the new value enters it (input gate = 1 - forget gate).
 
 Per head (H heads, d query channels, e value channels) a state S [d, e] that starts at zero and is
 carried from token to token:
@@ -6,8 +7,8 @@ carried from token to token:
     q_t = silu(W_q h_t)            f_t = l + (1 - l) * sigmoid(W_f h_t + b_f)         v_t = W_v h_t
     S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T                o_t = S_t^T q_t
 
-with l in [0, 1) a learned lower bound of the gate per head and channel (stored as it is used).  There is no
-key: 1 - f_t stands where a key would.  Each head's o_t is RMS-normalised over its e values with one weight
+with l in [0, 1) a learned lower bound of the gate per head and channel (stored as it is used).  The mixer has
+no key projection: 1 - f_t stands where a key would.  Each head's o_t is RMS-normalised over its e values with one weight
 vector [e] shared by the heads; the heads are concatenated and projected by W_o.
 
 The three projections are one contraction against the stacked [2*H*d + H*e, width] matrix whose result is

@@ -1,5 +1,6 @@
-"""Token shift on what a mixer reads: h_t <- h_t + (h_{t-1} - h_t) * mu per channel, with h_{t-1} the
-token before's h as it was before this replacement, and zeros before a sequence's first token.
+"""Token shift on a mixer's input: every channel of row t is moved towards the same channel of row t-1 by a
+learned fraction, h_t <- h_t + (h_{t-1} - h_t) * mu, where h_{t-1} is the UNSHIFTED row of the token before (a
+zero row ahead of a sequence's first token).
 
 `TokenShift` is a mixer that wraps a mixer.  It asks for the inner mixer's growing cache, and for ONE
 per-sequence state that holds its own row (the last token's unshifted h, float32) followed by whatever
