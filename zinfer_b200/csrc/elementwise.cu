@@ -376,22 +376,30 @@ __global__ void norm_shift_vec4_kernel(const float* __restrict__ x, const float*
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x;
-  const int b = tok_seq[t];
-  const bool first = t == cu_q[b];
   const int n4 = dim >> 2;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)t * dim);
-  const float4* xp = reinterpret_cast<const float4*>(x + (size_t)(first ? t : t - 1) * dim);
-  float4* st = reinterpret_cast<float4*>(state + (size_t)seq_slot[b] * state_stride);
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f), one = make_float4(1.f, 1.f, 1.f, 1.f);
   float4 vx[4], vp[4], vw[4], vm[4];
+  // the row itself, the weights and the shift need no index: they are asked for first
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int d = threadIdx.x + i * blockDim.x;
     const bool in = d < n4;
     vx[i] = in ? xr[d] : zero;
-    vp[i] = in ? (first ? st[d] : xp[d]) : zero;
     vw[i] = (in && w) ? reinterpret_cast<const float4*>(w)[d] : one;
     vm[i] = in ? reinterpret_cast<const float4*>(mu)[d] : zero;
+  }
+  // a sequence's tokens lie side by side in the batch: a token is its sequence's first of this step exactly
+  // when the row before belongs to another sequence (two loads that do not wait for one another; the slot,
+  // a third one behind them, is needed only by a first token or when the state is written)
+  const int b = tok_seq[t];
+  const bool first = t == 0 || tok_seq[t - 1] != b;
+  const float4* xp = reinterpret_cast<const float4*>(x + (size_t)(first ? t : t - 1) * dim);
+  float4* st = (first || write_state) ? reinterpret_cast<float4*>(state + (size_t)seq_slot[b] * state_stride) : nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    vp[i] = d < n4 ? (first ? st[d] : xp[d]) : zero;
   }
   float sc = 1.f, sp = 1.f;
   if (w) {
