@@ -233,6 +233,10 @@ def plain_attention(kind, x, t, H, G, d, vd, scale, rot, eps=2e-6):
     ("attention_2", 128, 4, 4, 64, 64, 0.11, (500.0, 32), 64),
     ("attention_2", 64, 1, 1, 16, 16, 0.25, None, 16),           # a single head: the mix is one number
     ("attention_2", 96, 6, 2, 48, 40, 0.14, (10000.0, 48), 32),
+    ("attention", 64, 4, 2, 32, 32, 0.18, (10000.0, 16), 32),    # head widths that the one-lane-per-key single-token kernel takes
+    ("attention", 96, 2, 1, 96, 96, 0.1, (300.0, 96), 32),
+    ("attention_2", 128, 4, 2, 128, 128, 0.09, (10000.0, 64), 64),   # mixed heads on the mma.sync kernels of width 128
+    ("attention_2", 64, 8, 8, 64, 64, 0.12, None, 64),               # eight value heads for every head's weights
 ])
 def test_attention_kinds_alone(k, dtype, kind, D, H, G, d, vd, scale, rot, page):
     t = attention_tensors(D, H, G, d, vd, dtype, 70)
