@@ -152,7 +152,7 @@ def plain_hgrn2(x, t, H, d, e, eps):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,H,d,e", [(40, 2, 8, 12), (32, 1, 4, 4), (38, 3, 5, 9), (128, 2, 64, 64), (64, 1, 128, 32),
-                                     (48, 1, 160, 16), (64, 2, 16, 200)])
+                                     (48, 1, 160, 16), (64, 2, 16, 200), (32, 1, 300, 40)])
 def test_hgrn2_part(k, dtype, D, H, d, e):
     """Three sequences: a prompt step of unequal portions, then single tokens; slots other than the batch index."""
     from zinfer_b200.parts import Hgrn2

@@ -20,7 +20,7 @@
 #include <math.h>
 
 #define HG_R 8             // warps of a block, each with a stretch of the d channels
-#define HG_MAX_D 256
+#define HG_MAX_D 512
 
 // In place on the rows of qfv: q <- silu(q), f <- lower + (1 - lower) * sigmoid(f + bias); v is left alone.
 __global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float* __restrict__ f_bias,
@@ -38,7 +38,7 @@ __global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float*
   }
 }
 
-// DPT: channels per warp; TT: tokens staged at once (sixteen, or eight where sixteen do not fit shared memory)
+// DPT: channels per warp; TT: tokens staged at once (sixteen, or eight or four where more do not fit shared memory)
 template <int DPT, int TT>
 __global__ void __launch_bounds__(HG_R * 32)
     hgrn2_scan_kernel(const float* __restrict__ qfv, int ld, float* __restrict__ state, long long state_stride,
@@ -194,7 +194,7 @@ int zk_hgrn2_scan(float* qfv, int ld, const float* f_bias, const float* lower, f
   }
   dim3 grid(n_seqs, H, (e + 31) / 32);
 #define ZK_HG(DP)                                                                                                    \
-  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 16 ? 8 : 16)>, grid, dim3(HG_R * 32), 0, stream, (const float*)qfv, ld, \
+  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 32 ? 4 : (DP > 16 ? 8 : 16))>, grid, dim3(HG_R * 32), 0, stream, (const float*)qfv, ld, \
                              state, state_stride, o, cu_q, seq_slot, H, d, e)
   const int dpt = (d + HG_R - 1) / HG_R;
   if (dpt <= 1) ZK_HG(1);
@@ -202,7 +202,8 @@ int zk_hgrn2_scan(float* qfv, int ld, const float* f_bias, const float* lower, f
   if (dpt <= 4) ZK_HG(4);
   if (dpt <= 8) ZK_HG(8);
   if (dpt <= 16) ZK_HG(16);
-  ZK_HG(32);
+  if (dpt <= 32) ZK_HG(32);
+  ZK_HG(64);
 #undef ZK_HG
 }
 
